@@ -1,0 +1,359 @@
+// HBM-bound kernels of the Muon hot path: Frobenius normalisation (with the transposed copy the
+// GEMMs need), fused momentum + Nesterov, fused weight decay + scaled update.  All use 16-byte
+// global accesses and grid sizes tied to the SM count; arithmetic keeps the reference's rounding
+// points (torch's element kernels compute in fp32 and round once per op).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace fm {
+namespace {
+
+constexpr int kNormBlocks = 1024;  // upper bound of partial sums (floats of scratch)
+
+template <typename T> __device__ __forceinline__ float ld_f(T v);
+template <> __device__ __forceinline__ float ld_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float ld_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float ld_f<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T st_f(float v);
+template <> __device__ __forceinline__ float st_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 st_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half st_f<__half>(float v) { return __float2half_rn(v); }
+
+// value of the input after the reference's `G.bfloat16()` (flash_muon/muon.py:15)
+template <typename T>
+__device__ __forceinline__ float as_bf16_value(T v) {
+  return __bfloat162float(__float2bfloat16_rn(ld_f<T>(v)));
+}
+
+__device__ __forceinline__ float block_sum_256(float v, float* red /* 8 floats */) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) s += red[w];  // same order in every thread and every block
+  return s;
+}
+
+// ---------------------------------------------------------------- sum of squares, partials
+template <typename T>
+__global__ void __launch_bounds__(256)
+sumsq_partial_kernel(const T* __restrict__ g, long long rows, long long cols, long long ldg,
+                     int vec_ok, float* __restrict__ partials) {
+  __shared__ float red[8];
+  constexpr int V = 16 / sizeof(T);
+  float s = 0.f;
+  const long long n = rows * cols;
+  if (vec_ok) {  // contiguous, 16-byte aligned, n % V == 0
+    const long long nv = n / V;
+    const uint4* g4 = reinterpret_cast<const uint4*>(g);
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < nv;
+         i += (long long)gridDim.x * 256) {
+      const uint4 raw = __ldg(g4 + i);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float f = as_bf16_value<T>(e[j]);
+        s = fmaf(f, f, s);
+      }
+    }
+  } else {
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n;
+         i += (long long)gridDim.x * 256) {
+      const long long r = i / cols, c = i - r * cols;
+      const float f = as_bf16_value<T>(g[r * ldg + c]);
+      s = fmaf(f, f, s);
+    }
+  }
+  const float tot = block_sum_256(s, red);
+  if (threadIdx.x == 0) partials[blockIdx.x] = tot;
+}
+
+// ---------------------------------------------------------------- scale + transposed copy
+// One 64x64 tile of G per block.  Every block first folds the partial sums in one fixed order, so
+// all blocks derive the same denominator without a third launch.
+template <typename T>
+__global__ void __launch_bounds__(256)
+scale_transpose_kernel(const T* __restrict__ g, long long rows, long long cols, long long ldg,
+                       const float* __restrict__ partials, int nparts,
+                       __nv_bfloat16* __restrict__ xd, long long ldxd,
+                       __nv_bfloat16* __restrict__ xt, long long ldxt) {
+  __shared__ float red[8];
+  __shared__ __nv_bfloat16 tile[64][66];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += 256) s += partials[i];
+  const float total = block_sum_256(s, red);
+  // torch: norm -> bf16, (+1e-7) -> bf16, x / that -> bf16  (flash_muon/muon.py:23)
+  const float d = __bfloat162float(__float2bfloat16_rn(sqrtf(total)));
+  const float dp = __bfloat162float(__float2bfloat16_rn(d + 1e-7f));
+
+  const long long tiles_c = (cols + 63) / 64;
+  const long long tr = blockIdx.x / tiles_c, tc = blockIdx.x - tr * tiles_c;
+  const long long r0 = tr * 64, c0 = tc * 64;
+  {
+    const int rr = threadIdx.x >> 2, cs = (threadIdx.x & 3) * 16;
+    const long long r = r0 + rr;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const long long c = c0 + cs + e;
+      __nv_bfloat16 q = __float2bfloat16_rn(0.f);
+      if (r < rows && c < cols) {
+        q = __float2bfloat16_rn(as_bf16_value<T>(g[r * ldg + c]) / dp);
+        if (xd) xd[r * ldxd + c] = q;
+      }
+      tile[rr][cs + e] = q;
+    }
+  }
+  if (xt == nullptr) return;
+  __syncthreads();
+  {
+    const int cc = threadIdx.x >> 2, rs = (threadIdx.x & 3) * 16;
+    const long long c = c0 + cc;
+    if (c < cols) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const long long r = r0 + rs + e;
+        if (r < rows) xt[c * ldxt + r] = tile[rs + e][cc];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- momentum + Nesterov
+// torch's lerp (element kernel in fp32): w < 0.5 ? a + w*(b-a) : b - (b-a)*(1-w)
+__device__ __forceinline__ float lerp_f(float a, float b, float w) {
+  return (fabsf(w) < 0.5f) ? a + w * (b - a) : b - (b - a) * (1.f - w);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+momentum_kernel(T* __restrict__ grad, T* __restrict__ buf, long long n, float w_buf, float w_grad,
+                int nesterov, int vec_ok) {
+  constexpr int V = 16 / sizeof(T);
+  const long long stride = (long long)gridDim.x * 256;
+  if (vec_ok) {
+    const long long nv = n / V;
+    uint4* g4 = reinterpret_cast<uint4*>(grad);
+    uint4* b4 = reinterpret_cast<uint4*>(buf);
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < nv; i += stride) {
+      uint4 graw = g4[i], braw = b4[i];
+      T* ge = reinterpret_cast<T*>(&graw);
+      T* be = reinterpret_cast<T*>(&braw);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float gv = ld_f<T>(ge[j]);
+        const T nb = st_f<T>(lerp_f(ld_f<T>(be[j]), gv, w_buf));
+        be[j] = nb;
+        if (nesterov) ge[j] = st_f<T>(lerp_f(gv, ld_f<T>(nb), w_grad));
+      }
+      b4[i] = braw;
+      if (nesterov) g4[i] = graw;
+    }
+    // tail
+    for (long long i = nv * V + (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+      const float gv = ld_f<T>(grad[i]);
+      const T nb = st_f<T>(lerp_f(ld_f<T>(buf[i]), gv, w_buf));
+      buf[i] = nb;
+      if (nesterov) grad[i] = st_f<T>(lerp_f(gv, ld_f<T>(nb), w_grad));
+    }
+  } else {
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+      const float gv = ld_f<T>(grad[i]);
+      const T nb = st_f<T>(lerp_f(ld_f<T>(buf[i]), gv, w_buf));
+      buf[i] = nb;
+      if (nesterov) grad[i] = st_f<T>(lerp_f(gv, ld_f<T>(nb), w_grad));
+    }
+  }
+}
+
+// ---------------------------------------------------------------- decay + update, multi-tensor
+// torch: mul_(scalar) is one fp32 multiply, add_(u, alpha) is a + alpha*b contracted to one fma;
+// the intrinsics pin that shape so fp32 parameters (no rounding in between) match bit for bit.
+constexpr int kMaxTensors = 32;
+struct UpdateTable {
+  void* p[kMaxTensors];
+  const void* u[kMaxTensors];
+  long long n[kMaxTensors];
+  float alpha[kMaxTensors];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+update_kernel(const UpdateTable tab, float decay) {
+  constexpr int V = 8;  // elements per iteration: one 16-byte load of the bf16 update
+  const int ti = blockIdx.y;
+  T* __restrict__ p = reinterpret_cast<T*>(tab.p[ti]);
+  const __nv_bfloat16* __restrict__ u = reinterpret_cast<const __nv_bfloat16*>(tab.u[ti]);
+  const long long n = tab.n[ti];
+  const float alpha = tab.alpha[ti];
+  const long long stride = (long long)gridDim.x * 256;
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(u) & 15u) == 0);
+  long long done = 0;
+  if (vec_ok) {
+    const long long nv = n / V;
+    const uint4* u4 = reinterpret_cast<const uint4*>(u);
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < nv; i += stride) {
+      const uint4 uraw = __ldg(u4 + i);
+      const __nv_bfloat16* ue = reinterpret_cast<const __nv_bfloat16*>(&uraw);
+      alignas(16) T pv[V];
+      if (sizeof(T) == 2) {
+        *reinterpret_cast<uint4*>(pv) = reinterpret_cast<uint4*>(p)[i];
+      } else {
+        reinterpret_cast<uint4*>(pv)[0] = reinterpret_cast<uint4*>(p)[2 * i];
+        reinterpret_cast<uint4*>(pv)[1] = reinterpret_cast<uint4*>(p)[2 * i + 1];
+      }
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const T dec = st_f<T>(__fmul_rn(ld_f<T>(pv[j]), decay));
+        pv[j] = st_f<T>(__fmaf_rn(alpha, __bfloat162float(ue[j]), ld_f<T>(dec)));
+      }
+      if (sizeof(T) == 2) {
+        reinterpret_cast<uint4*>(p)[i] = *reinterpret_cast<uint4*>(pv);
+      } else {
+        reinterpret_cast<uint4*>(p)[2 * i] = reinterpret_cast<uint4*>(pv)[0];
+        reinterpret_cast<uint4*>(p)[2 * i + 1] = reinterpret_cast<uint4*>(pv)[1];
+      }
+    }
+    done = nv * V;
+  }
+  for (long long i = done + (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+    const T dec = st_f<T>(__fmul_rn(ld_f<T>(p[i]), decay));
+    p[i] = st_f<T>(__fmaf_rn(alpha, __bfloat162float(u[i]), ld_f<T>(dec)));
+  }
+}
+
+int elementwise_grid(long long n, int per_thread) {
+  const long long want = (n + 256LL * per_thread - 1) / (256LL * per_thread);
+  const long long cap = (long long)sm_count() * 8;
+  long long g = want < cap ? want : cap;
+  return (int)(g < 1 ? 1 : g);
+}
+
+template <typename T>
+int normalize_t(const T* g, long long rows, long long cols, long long ldg, __nv_bfloat16* xd,
+                long long ldxd, __nv_bfloat16* xt, long long ldxt, float* partials,
+                cudaStream_t stream) {
+  const long long n = rows * cols;
+  constexpr int V = 16 / sizeof(T);
+  const int vec_ok = (ldg == cols) && ((reinterpret_cast<uintptr_t>(g) & 15u) == 0) && (n % V == 0);
+  long long nb = (n + 8191) / 8192;
+  if (nb > kNormBlocks) nb = kNormBlocks;
+  if (nb < 1) nb = 1;
+  sumsq_partial_kernel<T><<<(int)nb, 256, 0, stream>>>(g, rows, cols, ldg, vec_ok, partials);
+  FM_CUDA_CHECK(cudaGetLastError());
+  const long long tiles = ((rows + 63) / 64) * ((cols + 63) / 64);
+  if (tiles > 0x7fffffffLL) return fail(FM_ERR_UNSUPPORTED, "matrix too large");
+  scale_transpose_kernel<T><<<(int)tiles, 256, 0, stream>>>(g, rows, cols, ldg, partials, (int)nb,
+                                                            xd, ldxd, xt, ldxt);
+  FM_CUDA_CHECK(cudaGetLastError());
+  return FM_OK;
+}
+
+}  // namespace
+}  // namespace fm
+
+extern "C" size_t fm_norm_scratch_floats(void) { return fm::kNormBlocks; }
+
+extern "C" int fm_normalize(const void* G, int64_t rows, int64_t cols, int64_t ldg, int g_dtype,
+                            void* xd, int64_t ldxd, void* xt, int64_t ldxt, float* partials,
+                            void* stream) {
+  using namespace fm;
+  clear_error();
+  if (!G || !partials || (!xd && !xt)) return fail(FM_ERR_INVALID, "null pointer");
+  if (rows <= 0 || cols <= 0 || ldg < cols || (xd && ldxd < cols) || (xt && ldxt < rows))
+    return fail(FM_ERR_INVALID, "bad extents");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (g_dtype) {
+    case FM_BF16:
+      return normalize_t<__nv_bfloat16>((const __nv_bfloat16*)G, rows, cols, ldg,
+                                        (__nv_bfloat16*)xd, ldxd, (__nv_bfloat16*)xt, ldxt,
+                                        partials, st);
+    case FM_F16:
+      return normalize_t<__half>((const __half*)G, rows, cols, ldg, (__nv_bfloat16*)xd, ldxd,
+                                 (__nv_bfloat16*)xt, ldxt, partials, st);
+    case FM_F32:
+      return normalize_t<float>((const float*)G, rows, cols, ldg, (__nv_bfloat16*)xd, ldxd,
+                                (__nv_bfloat16*)xt, ldxt, partials, st);
+    default:
+      return fail(FM_ERR_UNSUPPORTED, "unknown dtype %d", g_dtype);
+  }
+}
+
+extern "C" int fm_momentum(void* grad, void* buf, int64_t n, int dtype, double momentum,
+                           int nesterov, void* stream) {
+  using namespace fm;
+  clear_error();
+  if (!grad || !buf) return fail(FM_ERR_INVALID, "null pointer");
+  if (n < 0) return fail(FM_ERR_INVALID, "negative element count");
+  if (n == 0) return FM_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the reference passes python floats: lerp_(g, 1 - momentum) and lerp_(buf, momentum)
+  const float w_buf = (float)(1.0 - momentum);
+  const float w_grad = (float)momentum;
+  const int vec_ok = ((reinterpret_cast<uintptr_t>(grad) & 15u) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(buf) & 15u) == 0);
+  const int grid = elementwise_grid(n, dtype == FM_F32 ? 4 : 8);
+  switch (dtype) {
+    case FM_BF16:
+      momentum_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16*)grad, (__nv_bfloat16*)buf,
+                                                           n, w_buf, w_grad, nesterov, vec_ok);
+      break;
+    case FM_F16:
+      momentum_kernel<__half><<<grid, 256, 0, st>>>((__half*)grad, (__half*)buf, n, w_buf, w_grad,
+                                                    nesterov, vec_ok);
+      break;
+    case FM_F32:
+      momentum_kernel<float><<<grid, 256, 0, st>>>((float*)grad, (float*)buf, n, w_buf, w_grad,
+                                                   nesterov, vec_ok);
+      break;
+    default:
+      return fail(FM_ERR_UNSUPPORTED, "unknown dtype %d", dtype);
+  }
+  FM_CUDA_CHECK(cudaGetLastError());
+  return FM_OK;
+}
+
+extern "C" int fm_update_multi(void* const* params, const void* const* updates,
+                               const int64_t* numels, const double* alphas, int count, int p_dtype,
+                               double decay, void* stream) {
+  using namespace fm;
+  clear_error();
+  if (count < 0) return fail(FM_ERR_INVALID, "negative tensor count");
+  if (count == 0) return FM_OK;
+  if (!params || !updates || !numels || !alphas) return fail(FM_ERR_INVALID, "null table");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int base = 0; base < count; base += kMaxTensors) {
+    const int m = (count - base) < kMaxTensors ? (count - base) : kMaxTensors;
+    UpdateTable tab;
+    long long nmax = 0;
+    for (int i = 0; i < m; ++i) {
+      if (!params[base + i] || !updates[base + i] || numels[base + i] < 0)
+        return fail(FM_ERR_INVALID, "bad entry %d of the update table", base + i);
+      tab.p[i] = params[base + i];
+      tab.u[i] = updates[base + i];
+      tab.n[i] = numels[base + i];
+      tab.alpha[i] = (float)alphas[base + i];
+      if (tab.n[i] > nmax) nmax = tab.n[i];
+    }
+    if (nmax == 0) continue;
+    int gx = elementwise_grid(nmax, 8);
+    // share the SMs between the tensors of the launch
+    gx = (gx + m - 1) / m;
+    if (gx < 1) gx = 1;
+    const dim3 grid((unsigned)gx, (unsigned)m);
+    switch (p_dtype) {
+      case FM_BF16: update_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(tab, (float)decay); break;
+      case FM_F16: update_kernel<__half><<<grid, 256, 0, st>>>(tab, (float)decay); break;
+      case FM_F32: update_kernel<float><<<grid, 256, 0, st>>>(tab, (float)decay); break;
+      default: return fail(FM_ERR_UNSUPPORTED, "unknown dtype %d", p_dtype);
+    }
+    FM_CUDA_CHECK(cudaGetLastError());
+  }
+  return FM_OK;
+}

@@ -1,0 +1,414 @@
+// Tensor-core GEMM family of the Muon hot path for sm_100a:
+//   C[M,N] = A[M,K] * B[N,K]^T  (both operands row-major = K-major), fp32 accumulation in TMEM,
+//   fused epilogue  out = round(round(alpha*D) + round(beta*round(acc)))  and an optional
+//   transposed second store.
+// With sym != 0 the kernel is the symmetric rank-k update X X^T: a persistent scheduler walks
+// only the tile pairs on or above the diagonal and the epilogue writes every tile twice
+// (direct + mirrored) from the same rounded registers, so the result is bitwise symmetric.
+// It stands in for the reference's Triton kernel (flash_muon/matmul_transpose_triton.py:19-75)
+// and for the cuBLAS call + elementwise kernels of flash_muon/muon.py:27-29.
+//
+// Structure of one CTA (192 threads, one CTA per SM, persistent over a static tile list):
+//   warp 0     : TMA producer  (one lane) -- 64-column operand slabs into a ring of smem stages
+//   warp 1     : MMA issuer    (one lane) -- tcgen05.mma 128 x ncols x 16, accumulators in TMEM,
+//                double-buffered so the epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2..5 : epilogue -- tcgen05.ld 32 lanes x 32 columns, rounding-faithful arithmetic,
+//                global stores (direct rows + transposed columns)
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
+#include "common.cuh"
+#include "gemm_tc.cuh"
+#include "ptx.cuh"
+
+namespace fm {
+
+namespace {
+
+constexpr int BM = 128;          // rows of an output tile = UMMA M
+constexpr int BK = 64;           // K extent of one smem stage: 64 x 2 B = one 128-byte swizzle row
+constexpr int UMMA_K = 16;       // K of one tcgen05.mma for 16-bit operands
+constexpr int kThreads = 192;
+constexpr int kSlabBytes = 128 * BK * 2;  // one 128-row operand slab = one TMA box (16 KiB)
+
+struct GemmParams {
+  int M, N, K;
+  int sym;        // 1: triangular schedule + mirrored store (requires A == B, M == N)
+  int tiles_m;    // ceil(M / 128)
+  int num_tiles;  // length of the static tile list
+  int num_kb;     // ceil(K / 64)
+  const void* D;  // optional addend, row-major, unit column stride
+  long long ldd;
+  void* C;        // direct output (may be null): C[r*ldc_r + c*ldc_c]
+  long long ldc_r, ldc_c;
+  void* CT;       // transposed output (may be null): element (r,c) goes to CT[c*ldt_r + r*ldt_c]
+  long long ldt_r, ldt_c;
+  float alpha, beta;
+  int precise;    // 1: single rounding of alpha*D + beta*acc
+  int d_vec;      // D rows can be read with 16-byte loads
+  int c_vec;      // C rows can be written with 16-byte stores
+  unsigned int* err;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStageBytes = kSlabBytes + BN * BK * 2;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators of BN fp32 columns
+  static constexpr int kNumBars = 2 * kStages + 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kNumBars * 8 + 16 + 1024;
+};
+
+struct Tile {
+  int m0;     // first output row
+  int n0;     // first output column
+  int ncols;  // 128 or 256 (UMMA N)
+  int bi;     // 128-row block index (for the diagonal test)
+};
+
+// Tiles before column super-tile j of the triangular schedule (R = BN / 128).
+template <int R>
+__host__ __device__ __forceinline__ long long tri_before(long long j) {
+  return R == 1 ? j * (j + 1) / 2 : j * (j + 1);
+}
+
+template <int BN>
+__device__ __forceinline__ Tile decode_tile(const GemmParams& p, int t) {
+  constexpr int R = BN / 128;
+  Tile o;
+  int nblk0;
+  if (!p.sym) {
+    const int tn = t / p.tiles_m;
+    const int tm = t - tn * p.tiles_m;
+    o.m0 = tm * BM;
+    o.bi = tm;
+    nblk0 = tn * R;
+    o.ncols = BN;
+  } else {
+    // Column super-tile j owns row blocks i in [0, min(R*j + R, tiles_m)); only the last column
+    // can be clipped, so tri_before() is exact for every column start.
+    int j = R == 1 ? (int)((sqrtf(8.f * (float)t + 1.f) - 1.f) * 0.5f)
+                   : (int)((sqrtf(4.f * (float)t + 1.f) - 1.f) * 0.5f);
+    while (tri_before<R>(j + 1) <= t) ++j;
+    while (tri_before<R>(j) > t) --j;
+    const int i = t - (int)tri_before<R>(j);
+    o.m0 = i * BM;
+    o.bi = i;
+    const int sub = (i > R * j) ? (i - R * j) : 0;  // leading 128-column blocks below the diagonal
+    nblk0 = R * j + sub;
+    o.ncols = BN - sub * 128;
+  }
+  o.n0 = nblk0 * 128;
+  const int left = p.N - o.n0;  // > 0 by construction
+  if (left <= 128 && o.ncols > 128) o.ncols = 128;
+  return o;
+}
+
+template <typename T>
+struct Num;
+template <>
+struct Num<__nv_bfloat16> {
+  static constexpr uint32_t kFormat = 1;
+  static __device__ __forceinline__ __nv_bfloat16 rn(float f) { return __float2bfloat16_rn(f); }
+  static __device__ __forceinline__ float f(__nv_bfloat16 v) { return __bfloat162float(v); }
+};
+template <>
+struct Num<__half> {
+  static constexpr uint32_t kFormat = 0;
+  static __device__ __forceinline__ __half rn(float f) { return __float2half_rn(f); }
+  static __device__ __forceinline__ float f(__half v) { return __half2float(v); }
+};
+
+template <typename T, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint32_t bar_base = smem_base + C::kStages * C::kStageBytes;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kStages * C::kStageBytes + C::kNumBars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C::kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * C::kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * C::kStages + 2 + a); };
+  auto a_smem = [&](int s) { return smem_base + s * C::kStageBytes; };
+  auto b_smem = [&](int s) { return smem_base + s * C::kStageBytes + kSlabBytes; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 128);
+    }
+    *abort_flag = 0;
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&tmA);
+    ptx::prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+        const Tile tl = decode_tile<BN>(p, t);
+        const int nb = tl.ncols >> 7;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+          ptx::mbar_expect_tx(full_bar(s), (uint32_t)(1 + nb) * kSlabBytes);
+          ptx::tma_load_2d(a_smem(s), &tmA, full_bar(s), kb * BK, tl.m0);
+          for (int q = 0; q < nb; ++q)
+            ptx::tma_load_2d(b_smem(s) + q * kSlabBytes, &tmB, full_bar(s), kb * BK,
+                             tl.n0 + q * 128);
+          if (++s == C::kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+        const Tile tl = decode_tile<BN>(p, t);
+        if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        const uint32_t idesc = ptx::make_idesc_f16(Num<T>::kFormat, BM, (uint32_t)tl.ncols);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_smem(s));
+          const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_smem(s));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K by 16 elements = 32 bytes inside the swizzled row = +2 in the
+            // (address >> 4) field of the descriptor
+            ptx::umma_f16(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
+                          (uint32_t)((kb | k) != 0));
+          }
+          ptx::umma_commit(empty_bar(s));  // frees the stage when these MMAs have read it
+          if (++s == C::kStages) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::umma_commit(tfull_bar(acc));  // accumulator complete
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------- epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    T* const Cp = reinterpret_cast<T*>(p.C);
+    T* const CTp = reinterpret_cast<T*>(p.CT);
+    const T* const Dp = reinterpret_cast<const T*>(p.D);
+    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+      const Tile tl = decode_tile<BN>(p, t);
+      bool ok = ptx::mbar_wait(tfull_bar(acc), acc_ph, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      const int row = tl.m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const int nchunks = tl.ncols >> 5;
+      for (int ch = 0; ch < nchunks; ++ch) {
+        uint32_t raw[32];
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + ch * 32),
+                           raw);
+        ptx::tmem_ld_wait();
+        const int c0 = tl.n0 + ch * 32;
+        if (c0 >= p.N) continue;  // warp-uniform
+        const bool full_cols = (c0 + 32 <= p.N);
+        const bool diag = p.sym && ((c0 >> 7) == tl.bi);
+        alignas(16) T outv[32];
+        if (Dp != nullptr) {
+          alignas(16) T dv[32];
+          if (row_ok) {
+            const T* dptr = Dp + (long long)row * p.ldd + c0;
+            if (p.d_vec && full_cols) {
+              const uint4* d4 = reinterpret_cast<const uint4*>(dptr);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dv)[v] = __ldg(d4 + v);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) dv[j] = (c0 + j < p.N) ? dptr[j] : Num<T>::rn(0.f);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) dv[j] = Num<T>::rn(0.f);
+          }
+          if (p.precise) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              outv[j] = Num<T>::rn(fmaf(p.alpha, Num<T>::f(dv[j]), p.beta * __uint_as_float(raw[j])));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const T tacc = Num<T>::rn(__uint_as_float(raw[j]));
+              const T u = Num<T>::rn(p.alpha * Num<T>::f(dv[j]));
+              const T w = Num<T>::rn(p.beta * Num<T>::f(tacc));
+              outv[j] = Num<T>::rn(Num<T>::f(u) + Num<T>::f(w));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) outv[j] = Num<T>::rn(__uint_as_float(raw[j]));
+        }
+        if (row_ok) {
+          if (Cp != nullptr) {
+            if (p.c_vec && full_cols && !diag) {
+              uint4* c4 = reinterpret_cast<uint4*>(Cp + (long long)row * p.ldc_r + c0);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) c4[v] = reinterpret_cast<const uint4*>(outv)[v];
+            } else {
+              T* cptr = Cp + (long long)row * p.ldc_r + (long long)c0 * p.ldc_c;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int c = c0 + j;
+                if (c < p.N && (!diag || c >= row)) cptr[(long long)j * p.ldc_c] = outv[j];
+              }
+            }
+          }
+          if (CTp != nullptr) {
+            T* tptr = CTp + (long long)c0 * p.ldt_r + (long long)row * p.ldt_c;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int c = c0 + j;
+              if (c < p.N && (!diag || c > row)) tptr[(long long)j * p.ldt_r] = outv[j];
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1u;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*abort_flag) {
+    // Some wait ran out: give copies and MMAs still in flight a bounded time to land before the
+    // shared memory and TMEM of this CTA are released.
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 0x47450000u | (unsigned)blockIdx.x);
+}
+
+template <int BN>
+int count_tiles(int M, int N, int sym) {
+  constexpr int R = BN / 128;
+  const int tiles_m = (M + 127) / 128;
+  const int tiles_n = (N + BN - 1) / BN;
+  if (!sym) return tiles_m * tiles_n;
+  long long n = 0;
+  for (int j = 0; j < tiles_n; ++j) n += (R * j + R < tiles_m) ? (R * j + R) : tiles_m;
+  return (int)n;
+}
+
+template <typename T, int BN>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  FM_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    FM_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel<T, BN>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    configured[dev] = true;
+  }
+  p.num_tiles = count_tiles<BN>(p.M, p.N, p.sym);
+  const int sms = sm_count();
+  if (sms <= 0) return fail(FM_ERR_CUDA, "could not query the SM count");
+  const int grid = p.num_tiles < sms ? p.num_tiles : sms;
+  gemm_tc_kernel<T, BN><<<grid, kThreads, C::kSmemBytes, stream>>>(tmA, tmB, p);
+  FM_CUDA_CHECK(cudaGetLastError());
+  return FM_OK;
+}
+
+}  // namespace
+
+int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
+  if (a.dtype != FM_BF16 && a.dtype != FM_F16)
+    return fail(FM_ERR_UNSUPPORTED, "tensor-core GEMM covers bf16 and f16 only");
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.M > (1 << 30) || a.N > (1 << 30) || a.K > (1 << 30))
+    return fail(FM_ERR_INVALID, "bad GEMM extents M=%lld N=%lld K=%lld", (long long)a.M,
+                (long long)a.N, (long long)a.K);
+  if (!a.A || !a.B || (!a.C && !a.CT)) return fail(FM_ERR_INVALID, "null operand or no output");
+  if (a.sym && (a.M != a.N)) return fail(FM_ERR_INVALID, "symmetric mode needs M == N");
+
+  CUtensorMap tmA, tmB;
+  int rc = encode_tmap_2d(&tmA, a.dtype, a.A, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.lda, BK, 128);
+  if (rc != FM_OK) return rc;
+  rc = encode_tmap_2d(&tmB, a.dtype, a.B, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.ldb, BK, 128);
+  if (rc != FM_OK) return rc;
+
+  GemmParams p;
+  p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
+  p.sym = a.sym;
+  p.tiles_m = (p.M + 127) / 128;
+  p.num_kb = (p.K + BK - 1) / BK;
+  p.num_tiles = 0;
+  p.D = a.D; p.ldd = a.ldd;
+  p.C = a.C; p.ldc_r = a.ldc_r; p.ldc_c = a.ldc_c;
+  p.CT = a.CT; p.ldt_r = a.ldt_r; p.ldt_c = a.ldt_c;
+  p.alpha = a.alpha; p.beta = a.beta;
+  p.precise = a.precise;
+  p.d_vec = (a.D != nullptr) && ((reinterpret_cast<uintptr_t>(a.D) & 15u) == 0) && (a.ldd % 8 == 0);
+  p.c_vec = (a.C != nullptr) && ((reinterpret_cast<uintptr_t>(a.C) & 15u) == 0) &&
+            (a.ldc_c == 1) && (a.ldc_r % 8 == 0);
+  p.err = device_error_word();
+  if (!p.err) return fail(FM_ERR_CUDA, "no current CUDA device");
+
+  // Tile width: 256 columns (less operand traffic per FLOP) unless that leaves most SMs idle.
+  int bn = 256;
+  const int sms = sm_count();
+  if (count_tiles<256>(p.M, p.N, p.sym) < sms) bn = 128;
+  if (const char* e = getenv("FM_GEMM_BN")) {
+    const int v = atoi(e);
+    if (v == 128 || v == 256) bn = v;
+  }
+  if (a.dtype == FM_BF16)
+    return bn == 256 ? launch<__nv_bfloat16, 256>(tmA, tmB, p, stream)
+                     : launch<__nv_bfloat16, 128>(tmA, tmB, p, stream);
+  return bn == 256 ? launch<__half, 256>(tmA, tmB, p, stream)
+                   : launch<__half, 128>(tmA, tmB, p, stream);
+}
+
+}  // namespace fm

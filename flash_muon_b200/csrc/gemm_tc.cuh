@@ -1,0 +1,33 @@
+// Internal interface of the tcgen05 GEMM family (see gemm_tc.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace fm {
+
+struct GemmArgs {
+  int dtype = 0;             // FM_BF16 or FM_F16
+  const void* A = nullptr;   // [M,K] row-major, row pitch lda
+  int64_t lda = 0;
+  const void* B = nullptr;   // [N,K] row-major, row pitch ldb
+  int64_t ldb = 0;
+  int64_t M = 0, N = 0, K = 0;
+  int sym = 0;               // 1: A == B, triangular schedule, mirrored store through CT
+  const void* D = nullptr;   // optional addend [M,N], row pitch ldd
+  int64_t ldd = 0;
+  float alpha = 0.f, beta = 1.f;
+  int precise = 0;
+  void* C = nullptr;         // element (r,c) at C[r*ldc_r + c*ldc_c]
+  int64_t ldc_r = 0, ldc_c = 1;
+  void* CT = nullptr;        // element (r,c) at CT[c*ldt_r + r*ldt_c]
+  int64_t ldt_r = 0, ldt_c = 1;
+};
+
+// Validates, encodes the tensor maps and enqueues the kernel on `stream`.
+int gemm_tc(const GemmArgs& args, cudaStream_t stream);
+
+// Exact-fp32 FFMA symmetric rank-k update for f32 inputs and layouts TMA cannot address.
+int syrk_simt(const void* x, void* y, int64_t M, int64_t K, int64_t ldx, int64_t ldy_row,
+              int64_t ldy_col, int dtype, cudaStream_t stream);
+
+}  // namespace fm

@@ -1,0 +1,148 @@
+"""``Muon`` optimizer with the reference's constructor and ``step()`` (flash_muon/muon.py:36-110).
+
+Same parameter grouping (by ``numel``), same round-robin ownership (rank ``r`` owns
+``params[base + r]`` of every round), same order of operations and the same rounding points.
+What differs is how the device work is issued:
+
+* momentum + Nesterov is one fused kernel (``fm_momentum``) instead of two ``lerp_`` launches;
+* Newton-Schulz is one C-ABI call whose last GEMM epilogue writes the flat update straight into
+  this rank's slot of the gather buffer (no ``.flatten()`` copy, no staging tensor);
+* the gather buffer is double-buffered, so round ``i+1`` may fill its slot while round ``i`` is
+  still being gathered and applied;
+* the all-gather is in place (NCCL over NVLink via ``torch.distributed``), launched asynchronously
+  so that it overlaps the next round's Newton-Schulz exactly like the reference's
+  ``async_op=True`` call (flash_muon/muon.py:106-108);
+* weight decay + scaled update of all ``world_size`` parameters of a round is one multi-tensor
+  kernel (``fm_update_multi``) instead of ``2 * world_size`` launches.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from ._lib import check, current_stream_ptr, dtype_code, lib
+from .ops import fast_newtonschulz, newtonschulz_workspace_bytes
+
+__all__ = ["Muon"]
+
+
+class Muon(torch.optim.Optimizer):
+    """Muon - MomentUm Orthogonalized by Newton-schulz, data-parallel with round-robin ownership.
+
+    Arguments mirror ``flash_muon.Muon`` (flash_muon/muon.py:60), including ``weight_decay`` as
+    the third positional parameter:
+        lr, weight_decay, momentum, nesterov, ns_steps, rank, world_size.
+    With ``world_size == 1`` no process group is needed (the reference still calls the
+    collective); otherwise the default ``torch.distributed`` group must be initialised with NCCL.
+    """
+
+    def __init__(self, params, lr=0.02, weight_decay=0.01, momentum=0.95, nesterov=True,
+                 ns_steps=5, rank=None, world_size=None):
+        if (rank is None) or (world_size is None):
+            raise Exception("world_size and rank params required, if you want to use this optimizer on a single GPU, pass rank=0 and world_size=1.")
+        self.rank = rank
+        self.world_size = world_size
+        defaults = dict(lr=lr, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov,
+                        ns_steps=ns_steps)
+        params: list[Tensor] = [*params]
+        param_groups = []
+        # one group per distinct numel (flash_muon/muon.py:68); sorted so that every rank walks
+        # the groups in the same order whatever its hash seed
+        for size in sorted({p.numel() for p in params}):
+            b = torch.empty(world_size, size, dtype=torch.bfloat16, device="cuda")
+            b2 = torch.empty(world_size, size, dtype=torch.bfloat16, device="cuda")
+            group = dict(params=[p for p in params if p.numel() == size],
+                         update_buffer=b, update_buffer_views=[b[i] for i in range(world_size)],
+                         update_buffer_alt=b2,
+                         update_buffer_alt_views=[b2[i] for i in range(world_size)])
+            param_groups.append(group)
+        super().__init__(param_groups, defaults)
+        self._workspace: Tensor | None = None
+
+    # ------------------------------------------------------------------ helpers
+    def _ns_workspace(self, rows: int, cols: int, device) -> Tensor:
+        need = newtonschulz_workspace_bytes(rows, cols)
+        ws = self._workspace
+        if ws is None or ws.numel() < need or ws.device != device:
+            # sized once for the largest matrix this rank owns
+            biggest = need
+            for group in self.param_groups:
+                for i, p in enumerate(group["params"]):
+                    if i % self.world_size == self.rank and p.ndim >= 2:
+                        r = p.size(0)
+                        biggest = max(biggest, newtonschulz_workspace_bytes(r, p.numel() // r))
+            self._workspace = ws = torch.empty(biggest, dtype=torch.uint8, device=device)
+        return ws
+
+    @staticmethod
+    def _apply_updates(params_world, views, lr, weight_decay, stream_ptr):
+        # p *= 1 - lr*wd ; p += -lr*sqrt(max(1, rows/cols)) * g      (flash_muon/muon.py:87-89)
+        by_dtype: dict = {}
+        for p_world, g_world in zip(params_world, views):
+            assert p_world.is_contiguous(), "Muon parameters must be contiguous"
+            by_dtype.setdefault(p_world.dtype, []).append((p_world, g_world))
+        decay = 1 - lr * weight_decay
+        for dt, items in by_dtype.items():
+            n = len(items)
+            ptrs = (ctypes.c_void_p * n)(*[p.data_ptr() for p, _ in items])
+            upds = (ctypes.c_void_p * n)(*[g.data_ptr() for _, g in items])
+            nels = (ctypes.c_int64 * n)(*[p.numel() for p, _ in items])
+            alphas = (ctypes.c_double * n)(
+                *[-lr * max(1, p.size(-2) / p.size(-1)) ** 0.5 for p, _ in items])
+            check(lib.fm_update_multi(ptrs, upds, nels, alphas, n, dtype_code(dt), decay,
+                                      stream_ptr))
+
+    # ------------------------------------------------------------------ step
+    @torch.no_grad()
+    def step(self):
+        ws = self.world_size
+        for group in self.param_groups:
+            buffers = (group["update_buffer"], group["update_buffer_alt"])
+            views = (group["update_buffer_views"], group["update_buffer_alt_views"])
+            params: list[Tensor] = group["params"]
+            device = buffers[0].device
+            handle = None
+            params_world = None
+            prev = 0  # which buffer the round in flight uses
+
+            def update_prev():
+                if handle is not None:
+                    handle.wait()
+                self._apply_updates(params_world, views[prev], group["lr"], group["weight_decay"],
+                                    current_stream_ptr(device))
+
+            for round_idx, base_i in enumerate(range(0, len(params), ws)):
+                cur = round_idx & 1
+                slot = views[cur][self.rank]
+                if base_i + self.rank < len(params):
+                    p = params[base_i + self.rank]
+                    g = p.grad
+                    assert g is not None
+                    assert g.is_contiguous(), "Muon gradients must be contiguous"
+                    state = self.state[p]
+                    if "momentum_buffer" not in state:
+                        state["momentum_buffer"] = torch.zeros_like(g)
+                    buf: Tensor = state["momentum_buffer"]
+                    stream_ptr = current_stream_ptr(device)
+                    # buf.lerp_(g, 1 - momentum); g.lerp_(buf, momentum)  (muon.py:99-100)
+                    check(lib.fm_momentum(g.data_ptr(), buf.data_ptr(), g.numel(),
+                                          dtype_code(g.dtype), float(group["momentum"]),
+                                          1 if group["nesterov"] else 0, stream_ptr))
+                    g = g if group["nesterov"] else buf
+                    if g.ndim == 4:  # for the case of conv filters
+                        g = g.view(len(g), -1)
+                    rows, cols = g.shape
+                    fast_newtonschulz(g, steps=group["ns_steps"], out=slot.view(rows, cols),
+                                      workspace=self._ns_workspace(rows, cols, device))
+                # an idle rank contributes whatever its slot holds (muon.py:104-105)
+                if base_i > 0:
+                    update_prev()
+                if ws > 1:
+                    handle = dist.all_gather_into_tensor(buffers[cur], slot, async_op=True)
+                params_world = params[base_i: base_i + ws]
+                prev = cur
+            if params_world is not None:
+                update_prev()

@@ -1,0 +1,139 @@
+/*
+ * flash_muon_b200 -- C ABI of the B200 (sm_100a) Muon hot path.
+ *
+ * The reference project (nil0x9/flash-muon) is pure Python; its operator interface is
+ *   flash_muon/__init__.py:1-4   matmul_transpose, matmul_transpose_assign, fast_newtonschulz, Muon
+ * Each entry point below names the reference function whose device work it replaces.
+ *
+ * Conventions
+ *  - Every function returns an fm_status (0 = ok, negative = error).  Nothing throws.
+ *  - All data pointers are DEVICE pointers owned by the caller; nothing is allocated or freed
+ *    by the library and nothing synchronises unless stated.
+ *  - `stream` is a cudaStream_t passed as void* (0 = the legacy default stream).  All work of a
+ *    call is enqueued on that stream of the CURRENT device.
+ *  - Leading dimensions and strides are in ELEMENTS.
+ *  - Arguments are validated on the host before any launch.  fm_last_error() returns a
+ *    thread-local message for the last failing call of the calling thread.
+ */
+#ifndef FLASH_MUON_B200_H_
+#define FLASH_MUON_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  FM_OK = 0,
+  FM_ERR_INVALID = -1,     /* bad argument (null pointer, negative size, misaligned) */
+  FM_ERR_UNSUPPORTED = -2, /* dtype / shape outside what the kernels cover */
+  FM_ERR_CUDA = -3,        /* a CUDA runtime or driver call failed */
+  FM_ERR_DEVICE_WAIT = -4, /* a bounded wait inside a kernel ran out (see fm_device_status) */
+  FM_ERR_WORKSPACE = -5    /* workspace too small */
+} fm_status;
+
+typedef enum { FM_BF16 = 0, FM_F16 = 1, FM_F32 = 2 } fm_dtype;
+
+/* flags of fm_newtonschulz */
+enum {
+  FM_NS_FAITHFUL = 0, /* reproduce every intermediate rounding of the reference formulation */
+  FM_NS_PRECISE = 1   /* one rounding per fused epilogue (closer to exact, further from reference) */
+};
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int fm_version(void);
+
+/* Message of the last error raised on the calling thread ("" if none). */
+const char* fm_last_error(void);
+
+/*
+ * Synchronises the current device and reports whether any kernel of this library gave up a
+ * bounded wait since the last call (0 = none).  Clears the flag.  *code receives a word that
+ * identifies kernel, role and barrier.  No reference counterpart (the reference never checks
+ * device state); used by tests and by callers that want a post-step health check.
+ */
+int fm_device_status(unsigned int* code);
+
+/*
+ * y[M,M] = x[M,K] * x^T, fp32 accumulation, one rounding to `dtype`; only upper-triangular tile
+ * pairs are computed and every tile is also stored transposed, so y is bitwise symmetric.
+ * x is row-major with row pitch ldx and unit column stride; y is addressed as
+ * y[i*ldy_row + j*ldy_col] (arbitrary strides, as the reference passes them to its kernel).
+ * Replaces: mmt_kernel + matmul_transpose_assign, flash_muon/matmul_transpose_triton.py:19-101.
+ * bf16/f16 with ldx % 8 == 0 and a 16-byte aligned x run on tcgen05 tensor cores; f32 and other
+ * layouts run on an exact-fp32 FFMA kernel.
+ */
+int fm_syrk(const void* x, void* y, int64_t M, int64_t K, int64_t ldx, int64_t ldy_row,
+            int64_t ldy_col, int dtype, void* stream);
+
+/*
+ * General C[M,N] = A[M,K] * B[N,K]^T (+ fused epilogue), bf16/f16, both operands row-major with
+ * unit column stride (K-major).  out = round(round(alpha*D) + round(beta*round(acc))) when D is
+ * non-null (single rounding of alpha*D + beta*acc when `precise` != 0), round(acc) otherwise.
+ * C (direct, row pitch ldc) and CT (transposed copy, CT[j*ldct + i]) may each be null but not both.
+ * Building block of fm_newtonschulz (the reference's `B @ X` and `a*X + ...`,
+ * flash_muon/muon.py:29); exported for tests and benchmarks.
+ */
+int fm_gemm_nt(const void* A, int64_t lda, const void* B, int64_t ldb, int64_t M, int64_t N,
+               int64_t K, const void* D, int64_t ldd, float alpha, float beta, void* C,
+               int64_t ldc, void* CT, int64_t ldct, int dtype, int precise, void* stream);
+
+/*
+ * Symmetric rank-k update with the polynomial epilogue of the Newton-Schulz step:
+ * out = round(round(alpha*D) + round(beta*round(x x^T))) with D symmetric, out bitwise symmetric.
+ * Replaces matmul_transpose_assign(buf1, buf2) followed by `b*buf1 + c*buf2`,
+ * flash_muon/muon.py:27-28.
+ */
+int fm_syrk_poly(const void* x, int64_t ldx, int64_t M, int64_t K, const void* D, int64_t ldd,
+                 float alpha, float beta, void* out, int64_t ldo, int dtype, int precise,
+                 void* stream);
+
+/* Bytes of device workspace fm_newtonschulz needs for a rows x cols input (0 on bad sizes). */
+size_t fm_ns_workspace_bytes(int64_t rows, int64_t cols);
+
+/*
+ * out = Newton-Schulz orthogonalisation of G (rows x cols, row pitch ldg, dtype g_dtype), `steps`
+ * quintic iterations with (a,b,c) = (3.4445, -4.7750, 2.0315) after a Frobenius normalisation,
+ * all storage in bf16 and fp32 accumulation.  `out` is bf16 [rows, cols], contiguous, and must
+ * not alias G or the workspace.  Tall inputs (rows > cols) are iterated on transposed, as the
+ * reference does, without materialising a transposed copy per step.
+ * Replaces: fast_newtonschulz, flash_muon/muon.py:6-33.
+ */
+int fm_newtonschulz(const void* G, int64_t rows, int64_t cols, int64_t ldg, int g_dtype, int steps,
+                    void* out, void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/*
+ * Frobenius normalisation used by fm_newtonschulz, exported for tests:
+ * xd[rows,cols] (row pitch ldxd) = bf16(G) / (||bf16(G)||_F + 1e-7) and xt[cols,rows] (row pitch
+ * ldxt) = its transpose, with the reference's roundings (norm, sum and quotient each rounded to
+ * bf16).  `partials` is a device scratch of at least fm_norm_scratch_floats() floats that the
+ * call overwrites.  Either of xd / xt may be null.
+ * Replaces: `X / (X.norm(...) + 1e-7)`, flash_muon/muon.py:15-23.
+ */
+int fm_normalize(const void* G, int64_t rows, int64_t cols, int64_t ldg, int g_dtype, void* xd,
+                 int64_t ldxd, void* xt, int64_t ldxt, float* partials, void* stream);
+size_t fm_norm_scratch_floats(void);
+
+/*
+ * Momentum + Nesterov, in place, n elements of `dtype`:
+ *   buf <- lerp(buf, grad, 1 - momentum);  grad <- nesterov ? lerp(grad, buf, momentum) : grad
+ * each lerp rounded to `dtype` like torch's lerp_.  With nesterov == 0 grad is left untouched and
+ * the caller uses buf.  Replaces: flash_muon/muon.py:99-100.
+ */
+int fm_momentum(void* grad, void* buf, int64_t n, int dtype, double momentum, int nesterov,
+                void* stream);
+
+/*
+ * Fused decoupled weight decay + scaled update over `count` tensors in one launch:
+ *   p_i <- round(p_i * decay);  p_i <- round(p_i + alpha_i * u_i)      (u_i is bf16)
+ * params / updates are HOST arrays of device pointers.  Replaces: flash_muon/muon.py:87-89.
+ */
+int fm_update_multi(void* const* params, const void* const* updates, const int64_t* numels,
+                    const double* alphas, int count, int p_dtype, double decay, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASH_MUON_B200_H_ */
