@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 Muon hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One "step" is one ``Muon.step()`` over the Llama-3-8B-shaped matrix set of BASELINE.json
+(configs[4]: 32 layers x {q, o 4096x4096; k, v 1024x4096; gate, up 14336x4096; down 4096x14336},
+bf16, 224 matrices, 6.98e9 elements) -- the configuration the `Muon.step ms` half of the metric is
+quoted on; it fits one GPU.  N ranks share the work by the reference's round-robin ownership
+(strong scaling).  The `matmul_transpose TFLOP/s at 8192^2 bf16` half of the metric is measured by
+rank 0 at N=1 and rides in the same JSON line (`matmul_transpose`, `roofline`).
+
+The line also carries: `e2e` (same step with gradients coming from pinned host memory and the
+owned parameters copied back, copies inside the timed region), `cpu_baseline` (the oracle's CPU
+restatement of the reference on the box's host cores, bounded sample), `clocks` (nvidia-smi
+samples taken during the timed region) and `gpu_launches`.
+
+Data is synthetic (seeded normal values of the shapes above); no dataset is involved.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LLAMA_LAYER = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (14336, 4096),
+               (4096, 14336)]  # q k v o gate up down
+N_LAYERS = 32
+HP = dict(lr=0.02, weight_decay=0.01, momentum=0.95, nesterov=True, ns_steps=5)
+SYRK_DIM = 8192
+
+
+def ns_flops(rows: int, cols: int, steps: int = 5):
+    """(algorithmic, cuBLAS-equivalent) FLOPs of one Newton-Schulz call."""
+    m, k = min(rows, cols), max(rows, cols)
+    return steps * (m * (m + 1) * k + m * (m + 1) * m + 2 * m * m * k), steps * (4 * m * m * k + 2 * m ** 3)
+
+
+def measured_peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi samples of one GPU while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                       samples=len(sm))
+        return out
+
+
+# --------------------------------------------------------------------------- reference arm
+def cpu_reference_sample(threads: int):
+    """The oracle (CPU restatement of flash_muon/muon.py) on two matrices of the workload:
+    one k/v projection [1024x4096] and one q/o projection [4096x4096], full per-matrix work of a
+    step (momentum, Nesterov, 5 Newton-Schulz steps, decay + update).  Returns seconds and the
+    cuBLAS-equivalent FLOPs of the sample."""
+    from oracle import muon_oracle as O
+    torch.set_num_threads(threads)
+    shapes = [(1024, 4096), (4096, 4096)]
+    g = torch.Generator().manual_seed(0)
+    params = [(torch.randn(*s, generator=g) * 0.02).bfloat16() for s in shapes]
+    grads = [(torch.randn(*s, generator=g) * 1e-3).bfloat16() for s in shapes]
+    bufs = {}
+    t0 = time.perf_counter()
+    O.muon_step(params, grads, bufs, world_size=1, **HP)
+    dt = time.perf_counter() - t0
+    flops = sum(ns_flops(*s)[1] for s in shapes)
+    return dt, flops
+
+
+def full_step_flops():
+    alg = sum(ns_flops(*s)[0] for s in LLAMA_LAYER) * N_LAYERS
+    full = sum(ns_flops(*s)[1] for s in LLAMA_LAYER) * N_LAYERS
+    return alg, full
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    _, full = full_step_flops()
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, fl = cpu_reference_sample(threads)
+        if i >= args.warmup:
+            times.append(dt)
+    per_sample = sum(times) / len(times)
+    est_ms = per_sample * (full / fl) * 1e3
+    sample = ("oracle port on CPU: Muon.step work of one [1024x4096] and one [4096x4096] matrix per "
+              f"step, scaled to the 224-matrix set by cuBLAS-equivalent FLOPs (x{full / fl:.1f})")
+    line = {
+        "impl": "reference", "metric": "muon_step_ms", "value": est_ms, "unit": "ms",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": est_ms,
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "Muon.step on Llama-3-8B-shaped matrices (BASELINE configs[4])",
+                   "matrices": len(LLAMA_LAYER) * N_LAYERS, "ns_steps": 5, "device": "host cores"},
+        "cpu_baseline": {"value": est_ms, "unit": "ms", "cores": threads, "kind": "port",
+                         "sample": sample, "sample_seconds": per_sample},
+        "e2e": {"value": est_ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- our arm
+def time_syrk(peaks):
+    """matmul_transpose at 8192^2 bf16 on the current device, against cuBLAS x @ x.T interleaved in
+    the same process.  Input + output (268 MB) exceed L2, so no flush is needed between reps."""
+    import flash_muon_b200 as fm
+    m = k = SYRK_DIM
+    x = (torch.randn(m, k, device="cuda") / k ** 0.5).bfloat16()
+    y = torch.empty(m, m, device="cuda", dtype=torch.bfloat16)
+
+    def timed(fn, warm, rep):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(rep):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / rep
+
+    ours, cublas = [], []
+    for _ in range(3):  # interleave: clocks drift under load
+        ours.append(timed(lambda: fm.matmul_transpose_assign(x, y), 5, 30))
+        cublas.append(timed(lambda: torch.matmul(x, x.T, out=y), 5, 30))
+    t, tc = min(ours), min(cublas)
+    alg = m * (m + 1) * k
+    tiles = sum(min(2 * j + 2, m // 128) for j in range(m // 256))  # 128x256 tiles issued
+    execd = tiles * 2 * 128 * 256 * k
+    res = {"shape": [m, k], "ms": t, "tflops_effective": 2 * m * m * k / t / 1e9,
+           "tflops_algorithmic": alg / t / 1e9, "tflops_executed": execd / t / 1e9,
+           "cublas_ms": tc, "speedup_vs_cublas": tc / t, "reps": 30}
+    roof = {"kernel": "gemm_tc_kernel<bf16,256> as matmul_transpose 8192x8192", "bound": "tensor",
+            "achieved": alg / t / 1e9, "peak": peaks["bf16"], "unit": "TFLOP/s",
+            "frac": alg / t / 1e9 / peaks["bf16"], "frac_executed": execd / t / 1e9 / peaks["bf16"],
+            "traffic": None, "peak_source": f"{peaks['source']} burst (kernel timed alone)"}
+    return res, roof
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    import flash_muon_b200 as fm
+
+    rank = int(os.environ.get("RANK", "0"))
+    ws = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if ws > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=dev)
+    peaks = measured_peaks()
+
+    shapes = LLAMA_LAYER * N_LAYERS
+    g = torch.Generator(device=dev).manual_seed(0)  # same values on every rank (DP replicas)
+    params = [torch.nn.Parameter((torch.randn(*s, device=dev, generator=g) * 0.02).bfloat16())
+              for s in shapes]
+    for p in params:
+        p.grad = (torch.randn(p.shape, device=dev, generator=g) * 1e-3).bfloat16()
+    opt = fm.Muon(params, rank=rank, world_size=ws, **HP)
+
+    def sync():
+        if ws > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if ws == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    # ---- device-resident leg: gradients already in HBM
+    for _ in range(args.warmup):
+        opt.step()
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            opt.step()
+        e1.record()
+        sync()
+    ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    clocks = clk.summary()
+    fm._lib.device_status()
+
+    # ---- end-to-end leg: gradients arrive from pinned host memory, owned parameters go back
+    # ownership is per numel group: rank r owns params[base + r] of every round
+    owned = []
+    for grp in opt.param_groups:
+        for i, p in enumerate(grp["params"]):
+            if i % ws == rank:
+                owned.append(p)
+    host_g = {s: (torch.randn(*s) * 1e-3).bfloat16().pin_memory() for s in set(LLAMA_LAYER)}
+    host_p = {s: torch.empty(*s, dtype=torch.bfloat16).pin_memory() for s in set(LLAMA_LAYER)}
+    h2d = sum(p.numel() * 2 for p in owned)
+    d2h = h2d
+
+    def e2e_step():
+        for p in owned:
+            p.grad.copy_(host_g[tuple(p.shape)], non_blocking=True)
+        opt.step()
+        for p in owned:
+            host_p[tuple(p.shape)].copy_(p.detach(), non_blocking=True)
+
+    e2e_step()
+    sync()
+    k2 = max(1, min(args.steps, 3))
+    e0.record()
+    for _ in range(k2):
+        e2e_step()
+    e1.record()
+    sync()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / k2)
+
+    # launches of this library's kernels per step on this rank: per owned matrix 1 momentum,
+    # 2 normalisation, 3 GEMMs per Newton-Schulz step; per round one multi-tensor update
+    rounds = sum((len(grp["params"]) + ws - 1) // ws for grp in opt.param_groups)
+    launches_per_step = len(owned) * (1 + 2 + 3 * HP["ns_steps"]) + rounds
+    alg, full = full_step_flops()
+
+    line = {
+        "metric": "muon_step_ms", "value": ms, "unit": "ms", "n_gpus": ws, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "Muon.step on Llama-3-8B-shaped matrices (BASELINE configs[4])",
+                   "matrices": len(shapes), "elements": sum(a * b for a, b in shapes),
+                   "ns_steps": HP["ns_steps"], "parallelism": f"dp{ws} round-robin ownership",
+                   "l2": "working set (42+ GB) far larger than L2; no flush needed"},
+        "step_tflops_algorithmic": alg / ms / 1e9, "step_tflops_cublas_equivalent": full / ms / 1e9,
+        "step_frac_of_sustained_peak": alg / ms / 1e9 / ws / peaks["bf16_sustained"],
+        "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": k2, "note": "per rank: owned gradients from pinned host memory, owned parameters back"},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if ws == 1:
+        del params, opt
+        torch.cuda.empty_cache()
+        mt, roof = time_syrk(peaks)
+        line["matmul_transpose"] = mt
+        line["roofline"] = roof
+        threads = os.cpu_count() or 1
+        dt, fl = cpu_reference_sample(threads)
+        line["cpu_baseline"] = {
+            "value": dt * (full / fl) * 1e3, "unit": "ms", "cores": threads, "kind": "port",
+            "sample": ("oracle port: Muon.step work of one [1024x4096] and one [4096x4096] matrix, "
+                       f"scaled to the 224-matrix set by cuBLAS-equivalent FLOPs (x{full / fl:.1f})"),
+            "sample_seconds": dt}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if ws > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -39,6 +39,9 @@ class Muon(torch.optim.Optimizer):
     collective); otherwise the default ``torch.distributed`` group must be initialised with NCCL.
     """
 
+    # Device of the gather buffers ("cuda" = the current CUDA device, flash_muon/muon.py:69).
+    _buffer_device = "cuda"
+
     def __init__(self, params, lr=0.02, weight_decay=0.01, momentum=0.95, nesterov=True,
                  ns_steps=5, rank=None, world_size=None):
         if (rank is None) or (world_size is None):
@@ -52,8 +55,8 @@ class Muon(torch.optim.Optimizer):
         # one group per distinct numel (flash_muon/muon.py:68); sorted so that every rank walks
         # the groups in the same order whatever its hash seed
         for size in sorted({p.numel() for p in params}):
-            b = torch.empty(world_size, size, dtype=torch.bfloat16, device="cuda")
-            b2 = torch.empty(world_size, size, dtype=torch.bfloat16, device="cuda")
+            b = torch.empty(world_size, size, dtype=torch.bfloat16, device=self._buffer_device)
+            b2 = torch.empty(world_size, size, dtype=torch.bfloat16, device=self._buffer_device)
             group = dict(params=[p for p in params if p.numel() == size],
                          update_buffer=b, update_buffer_views=[b[i] for i in range(world_size)],
                          update_buffer_alt=b2,
@@ -77,9 +80,26 @@ class Muon(torch.optim.Optimizer):
             self._workspace = ws = torch.empty(biggest, dtype=torch.uint8, device=device)
         return ws
 
-    @staticmethod
-    def _apply_updates(params_world, views, lr, weight_decay, stream_ptr):
+    def _momentum(self, g: Tensor, buf: Tensor, momentum: float, nesterov: bool) -> Tensor:
+        # buf.lerp_(g, 1 - momentum); g.lerp_(buf, momentum)           (flash_muon/muon.py:99-100)
+        assert g.is_contiguous(), "Muon gradients must be contiguous"
+        check(lib.fm_momentum(g.data_ptr(), buf.data_ptr(), g.numel(), dtype_code(g.dtype),
+                              float(momentum), 1 if nesterov else 0, current_stream_ptr(g.device)))
+        return g if nesterov else buf
+
+    def _orthogonalize(self, g: Tensor, out: Tensor, steps: int) -> None:
+        # fast_newtonschulz(g, steps).flatten() written into `out`     (flash_muon/muon.py:103)
+        rows, cols = g.shape
+        fast_newtonschulz(g, steps=steps, out=out.view(rows, cols),
+                          workspace=self._ns_workspace(rows, cols, g.device))
+
+    def _all_gather(self, buffer: Tensor, slot: Tensor):
+        # in place: `slot` is row `rank` of `buffer`                    (flash_muon/muon.py:108)
+        return dist.all_gather_into_tensor(buffer, slot, async_op=True)
+
+    def _apply_updates(self, params_world, views, lr, weight_decay):
         # p *= 1 - lr*wd ; p += -lr*sqrt(max(1, rows/cols)) * g      (flash_muon/muon.py:87-89)
+        stream_ptr = current_stream_ptr(views[0].device)
         by_dtype: dict = {}
         for p_world, g_world in zip(params_world, views):
             assert p_world.is_contiguous(), "Muon parameters must be contiguous"
@@ -103,7 +123,6 @@ class Muon(torch.optim.Optimizer):
             buffers = (group["update_buffer"], group["update_buffer_alt"])
             views = (group["update_buffer_views"], group["update_buffer_alt_views"])
             params: list[Tensor] = group["params"]
-            device = buffers[0].device
             handle = None
             params_world = None
             prev = 0  # which buffer the round in flight uses
@@ -111,8 +130,7 @@ class Muon(torch.optim.Optimizer):
             def update_prev():
                 if handle is not None:
                     handle.wait()
-                self._apply_updates(params_world, views[prev], group["lr"], group["weight_decay"],
-                                    current_stream_ptr(device))
+                self._apply_updates(params_world, views[prev], group["lr"], group["weight_decay"])
 
             for round_idx, base_i in enumerate(range(0, len(params), ws)):
                 cur = round_idx & 1
@@ -121,27 +139,19 @@ class Muon(torch.optim.Optimizer):
                     p = params[base_i + self.rank]
                     g = p.grad
                     assert g is not None
-                    assert g.is_contiguous(), "Muon gradients must be contiguous"
                     state = self.state[p]
                     if "momentum_buffer" not in state:
                         state["momentum_buffer"] = torch.zeros_like(g)
                     buf: Tensor = state["momentum_buffer"]
-                    stream_ptr = current_stream_ptr(device)
-                    # buf.lerp_(g, 1 - momentum); g.lerp_(buf, momentum)  (muon.py:99-100)
-                    check(lib.fm_momentum(g.data_ptr(), buf.data_ptr(), g.numel(),
-                                          dtype_code(g.dtype), float(group["momentum"]),
-                                          1 if group["nesterov"] else 0, stream_ptr))
-                    g = g if group["nesterov"] else buf
+                    g = self._momentum(g, buf, group["momentum"], group["nesterov"])
                     if g.ndim == 4:  # for the case of conv filters
                         g = g.view(len(g), -1)
-                    rows, cols = g.shape
-                    fast_newtonschulz(g, steps=group["ns_steps"], out=slot.view(rows, cols),
-                                      workspace=self._ns_workspace(rows, cols, device))
+                    self._orthogonalize(g, slot, group["ns_steps"])
                 # an idle rank contributes whatever its slot holds (muon.py:104-105)
                 if base_i > 0:
                     update_prev()
                 if ws > 1:
-                    handle = dist.all_gather_into_tensor(buffers[cur], slot, async_op=True)
+                    handle = self._all_gather(buffers[cur], slot)
                 params_world = params[base_i: base_i + ws]
                 prev = cur
             if params_world is not None:

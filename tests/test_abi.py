@@ -1,0 +1,70 @@
+"""The C-ABI library loads and exports every symbol ``include/flash_muon_b200.h`` declares
+(no compute calls: this runs without a GPU)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "flash_muon_b200.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(fm_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_hot_path_entry_points():
+    syms = declared_symbols()
+    for name in ("fm_syrk", "fm_newtonschulz", "fm_momentum", "fm_update_multi", "fm_gemm_nt",
+                 "fm_syrk_poly", "fm_normalize", "fm_ns_workspace_bytes", "fm_device_status"):
+        assert name in syms
+
+
+def test_library_builds_in_tree():
+    from flash_muon_b200 import build
+    path = build.build()
+    assert path.exists() and path.parent == ROOT / "flash_muon_b200"
+
+
+@pytest.mark.parametrize("name", declared_symbols())
+def test_library_exports(name):
+    from flash_muon_b200 import _lib
+    assert hasattr(_lib.lib, name), f"{name} declared in the header but not exported"
+    assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+
+
+def test_ctypes_table_has_no_undeclared_entry():
+    from flash_muon_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+
+
+def test_host_only_calls():
+    """Entry points that touch no device."""
+    from flash_muon_b200 import _lib
+    lib = _lib.lib
+    assert lib.fm_version() >= 100
+    assert lib.fm_norm_scratch_floats() >= 1
+    assert lib.fm_ns_workspace_bytes(0, 4) == 0
+    m, k = 1024, 4096
+    need = lib.fm_ns_workspace_bytes(m, k)
+    assert need == lib.fm_ns_workspace_bytes(k, m)          # tall = wide transposed
+    assert need >= (4 * m * k + 2 * m * m) * 2              # X, XT double-buffered + A + B
+    # argument validation happens before any CUDA call
+    assert lib.fm_syrk(None, None, 4, 4, 4, 4, 1, 0, None) == -1
+    assert b"null" in lib.fm_last_error()
+    assert lib.fm_newtonschulz(None, 4, 4, 4, 0, 5, None, None, 0, 0, None) == -1
+    assert lib.fm_momentum(None, None, 4, 0, 0.95, 1, None) == -1
+    assert lib.fm_update_multi(None, None, None, None, -1, 0, 1.0, None) == -1
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    """No fallback: pointing the loader at a missing file raises ImportError."""
+    import importlib
+    import flash_muon_b200._lib as L
+    monkeypatch.setenv("FLASH_MUON_B200_LIB", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError, match="no CPU or Triton fallback"):
+        importlib.reload(L)
+    monkeypatch.delenv("FLASH_MUON_B200_LIB")
+    importlib.reload(L)

@@ -1,0 +1,78 @@
+"""The HBM-bound kernels against torch's own CUDA element kernels (what the reference launches at
+flash_muon/muon.py:23, :87-89, :99-100): bit-exact, and against the CPU oracle."""
+import ctypes
+
+import pytest
+import torch
+
+from flash_muon_b200 import _lib
+from flash_muon_b200._lib import check, dtype_code, lib
+from oracle import muon_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.bfloat16, torch.float16, torch.float32]
+
+
+def _rand(n, dt, scale, seed):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(n, device=DEV, generator=g) * scale).to(dt)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("nesterov", [True, False])
+@pytest.mark.parametrize("n,offset", [(1 << 20, 0), (12345, 0), (4099, 1), (1, 0), (7, 3)])
+def test_momentum_bit_exact(dt, nesterov, n, offset):
+    g = _rand(n + offset, dt, 1e-3, 1)[offset:]
+    b = _rand(n + offset, dt, 1e-3, 2)[offset:]
+    g_ref, b_ref = g.clone(), b.clone()
+    used = O.momentum_update(g_ref, b_ref, 0.95, nesterov)   # torch CUDA lerp_
+    check(lib.fm_momentum(g.data_ptr(), b.data_ptr(), n, dtype_code(dt), 0.95, int(nesterov), 0))
+    assert torch.equal(b, b_ref)
+    assert torch.equal(g, g_ref)
+    assert used.data_ptr() == (g_ref if nesterov else b_ref).data_ptr()
+    # CPU oracle: same formula, torch's CPU kernel may differ in the last bit of a few elements
+    gc, bc = _rand(n + offset, dt, 1e-3, 1)[offset:].cpu(), _rand(n + offset, dt, 1e-3, 2)[offset:].cpu()
+    O.momentum_update(gc, bc, 0.95, nesterov)
+    assert torch.allclose(b.cpu().float(), bc.float(), rtol=2 ** -7, atol=1e-9)
+    assert torch.allclose(g.cpu().float(), gc.float(), rtol=2 ** -7, atol=1e-9)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("count", [1, 8, 40])
+def test_update_multi_bit_exact(dt, count):
+    lr, wd = 0.02, 0.01
+    shapes = [(64, 24), (24, 64), (40, 40)]
+    ps = [_rand(s[0] * s[1], dt, 0.02, 10 + i).view(*s) for i in range(count) for s in [shapes[i % 3]]]
+    us = [_rand(p.numel(), torch.bfloat16, 1.0, 100 + i) for i, p in enumerate(ps)]
+    refs = [p.clone() for p in ps]
+    for p, u in zip(refs, us):
+        O.apply_update(p, u, lr, wd)                          # torch CUDA mul_ / add_
+    n = len(ps)
+    ptrs = (ctypes.c_void_p * n)(*[p.data_ptr() for p in ps])
+    upds = (ctypes.c_void_p * n)(*[u.data_ptr() for u in us])
+    nels = (ctypes.c_int64 * n)(*[p.numel() for p in ps])
+    alphas = (ctypes.c_double * n)(*[-lr * max(1, p.size(-2) / p.size(-1)) ** 0.5 for p in ps])
+    check(lib.fm_update_multi(ptrs, upds, nels, alphas, n, dtype_code(dt), 1 - lr * wd, 0))
+    for p, r in zip(ps, refs):
+        assert torch.equal(p, r)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("rows,cols", [(256, 512), (512, 256), (100, 72), (1, 8), (65, 63), (1024, 4096)])
+def test_normalize_bit_exact(dt, rows, cols):
+    G = _rand(rows * cols, dt, 1.0, rows + cols).view(rows, cols)
+    X = G.bfloat16()
+    ref = X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7)     # flash_muon/muon.py:15, :23
+    ldd, ldt = cols + 8, rows + 16                            # padded pitches
+    xd = torch.full((rows, ldd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    xt = torch.full((cols, ldt), float("nan"), device=DEV, dtype=torch.bfloat16)
+    part = torch.empty(lib.fm_norm_scratch_floats(), device=DEV, dtype=torch.float32)
+    check(lib.fm_normalize(G.data_ptr(), rows, cols, cols, dtype_code(dt), xd.data_ptr(), ldd,
+                           xt.data_ptr(), ldt, part.data_ptr(), 0))
+    # the norm is reduced in another order than torch's: allow the rare last-bit flip of the
+    # bf16 denominator, which moves every quotient by at most one bf16 ulp
+    assert torch.allclose(xd[:, :cols].float(), ref.float(), rtol=2 ** -7, atol=0)
+    assert torch.equal(xt[:, :rows], xd[:, :cols].T)
+    assert torch.isnan(xd[:, cols:]).all() and torch.isnan(xt[:, rows:]).all()
+    _lib.device_status()

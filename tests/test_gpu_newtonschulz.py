@@ -1,0 +1,135 @@
+"""Parity of the fused Newton-Schulz (one C-ABI call, tcgen05 GEMMs with fused epilogues) with
+the reference's golden outputs, the CPU oracle and the same formulation in plain torch on CUDA."""
+import pytest
+import torch
+
+import flash_muon_b200 as fm
+from flash_muon_b200 import _lib
+from conftest import rel_fro
+from inputs import NS_SHAPES, ns_input
+from oracle import muon_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+# north-star tolerance after 5 steps; earlier steps are tighter because bf16 differences in the
+# accumulation order are amplified step by step
+TOL_STEPS = {0: 4e-3, 1: 1e-2, 3: 2e-2, 5: 2e-2}
+
+
+def torch_cuda_ns(G, steps):
+    """flash_muon/muon.py:13-33 in plain torch ops on the GPU (cuBLAS bf16 products)."""
+    a, b, c = O.NS_COEFFS
+    X = G.bfloat16()
+    if G.size(-2) > G.size(-1):
+        X = X.mT
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7)
+    for _ in range(steps):
+        A = X @ X.mT
+        A2 = A @ A.mT
+        B = b * A + c * A2
+        X = a * X + B @ X
+    if G.size(-2) > G.size(-1):
+        X = X.mT
+    return X
+
+
+@pytest.mark.parametrize("shape", NS_SHAPES)
+@pytest.mark.parametrize("steps", [0, 1, 5])
+def test_golden_cases(golden, shape, steps):
+    G = ns_input(*shape)
+    out = fm.fast_newtonschulz(G.to(DEV), steps)
+    assert out.dtype == torch.bfloat16 and out.shape == G.shape
+    ref = golden[f"fast_newtonschulz/{shape[0]}x{shape[1]}/steps{steps}"]
+    # tiny matrices sit on a higher bf16 noise floor than the 4096^2 config the 2e-2 bar is set
+    # on: the reference's own two formulations differ by 3.5e-2 here (see test_oracle_golden)
+    tol = TOL_STEPS[steps] if steps < 5 else 4e-2
+    assert rel_fro(out, ref) <= tol
+    assert rel_fro(out, torch_cuda_ns(G.to(DEV), steps)) <= 2e-3
+    _lib.device_status()
+
+
+def test_config1_4096_bf16_5_steps():
+    """configs[1]: 4096x4096, N(0,1) from a seed, 5 steps, against the CPU oracle."""
+    G = torch.randn(4096, 4096, generator=torch.Generator().manual_seed(0))
+    out = fm.fast_newtonschulz(G.to(DEV).bfloat16(), 5)
+    ref_cpu = O.newtonschulz(G.bfloat16(), 5)
+    err = rel_fro(out, ref_cpu)
+    assert err <= 2e-2, err
+    assert rel_fro(out, torch_cuda_ns(G.to(DEV).bfloat16(), 5)) <= 2e-3
+    # per-step errors against the oracle, for the record of how the difference grows
+    for s in (1, 3):
+        assert rel_fro(fm.fast_newtonschulz(G.to(DEV), s), O.newtonschulz(G, s)) <= TOL_STEPS[s]
+    _lib.device_status()
+
+
+SHAPES = [(1024, 1024), (1024, 4096), (4096, 1024), (1000, 520), (520, 1000), (130, 70), (8, 8),
+          (1, 16), (16, 1), (257, 1031)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32, torch.float16])
+def test_shapes_and_dtypes_against_torch_cuda(shape, dt):
+    G = torch.randn(*shape, device=DEV, generator=torch.Generator(device=DEV).manual_seed(sum(shape))).to(dt)
+    for steps in (0, 1, 5):
+        out = fm.fast_newtonschulz(G, steps)
+        ref = torch_cuda_ns(G, steps)
+        assert not torch.isnan(out).any()
+        assert rel_fro(out, ref) <= 2e-2, (shape, dt, steps)
+    _lib.device_status()
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024), (1024, 4096), (4096, 1024)])
+def test_against_cpu_oracle(shape):
+    G = torch.randn(*shape, generator=torch.Generator().manual_seed(shape[0] + 3 * shape[1]))
+    out = fm.fast_newtonschulz(G.to(DEV), 5)
+    assert rel_fro(out, O.newtonschulz(G, 5)) <= 2.5e-2  # 1024-wide shapes: noise floor ~1.8e-2
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (4096, 14336), (14336, 4096)])
+def test_full_size_properties(shape):
+    """Llama-3-8B shapes: the result is an approximate orthogonalisation -- every singular value
+    of the 5-step iterate lies in the band the quintic maps [0,1] into."""
+    G = torch.randn(*shape, device=DEV, generator=torch.Generator(device=DEV).manual_seed(7)).bfloat16()
+    out = fm.fast_newtonschulz(G, 5)
+    assert out.shape == G.shape and not torch.isnan(out).any()
+    X = out.float() if shape[0] <= shape[1] else out.float().T
+    ev = torch.linalg.eigvalsh((X @ X.T).double())
+    assert ev.min() > 0.3 ** 2 and ev.max() < 1.3 ** 2, (ev.min().item(), ev.max().item())
+    assert rel_fro(out, torch_cuda_ns(G, 5)) <= 2e-2
+    assert torch.equal(out, fm.fast_newtonschulz(G, 5)), "run-to-run determinism"
+    _lib.device_status()
+
+
+def test_out_and_workspace_arguments():
+    G = torch.randn(512, 768, device=DEV)
+    ref = fm.fast_newtonschulz(G, 5)
+    out = torch.empty(512, 768, device=DEV, dtype=torch.bfloat16)
+    ws = torch.empty(fm.newtonschulz_workspace_bytes(512, 768), device=DEV, dtype=torch.uint8)
+    r = fm.fast_newtonschulz(G, 5, out=out, workspace=ws)
+    assert r.data_ptr() == out.data_ptr() and torch.equal(out, ref)
+    flat = torch.empty(512 * 768, device=DEV, dtype=torch.bfloat16)
+    fm.fast_newtonschulz(G, 5, out=flat, workspace=ws)          # a gather-buffer slot
+    assert torch.equal(flat.view(512, 768), ref)
+    with pytest.raises(AssertionError, match="workspace too small"):
+        fm.fast_newtonschulz(G, 5, workspace=ws[:1024])
+    rc = _lib.lib.fm_newtonschulz(G.data_ptr(), 512, 768, 768, 2, 5, out.data_ptr(), ws.data_ptr(),
+                                  1024, 0, 0)
+    assert rc == -5 and b"workspace" in _lib.lib.fm_last_error()
+
+
+def test_precise_mode_is_closer_to_fp64():
+    G = torch.randn(1024, 1024, device=DEV)
+
+    def truth(G, steps=5):
+        a, b, c = O.NS_COEFFS
+        X = G.bfloat16().double()
+        X = X / (X.norm() + 1e-7)
+        for _ in range(steps):
+            A = X @ X.T
+            X = a * X + (b * A + c * A @ A) @ X
+        return X
+    t = truth(G)
+    faithful = rel_fro(fm.fast_newtonschulz(G, 5), t)
+    precise = rel_fro(fm.fast_newtonschulz(G, 5, precise=True), t)
+    assert precise <= faithful * 1.05
+    assert precise <= 3e-2

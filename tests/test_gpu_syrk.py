@@ -1,0 +1,149 @@
+"""Parity of the CUDA symmetric product (through the C ABI) with the oracle, the reference's golden
+outputs and a plain torch product, on BASELINE's configs and on the edge cases the reference's
+kernel handles (sizes off the tile grid, strided outputs, other dtypes)."""
+import os
+
+import pytest
+import torch
+
+import flash_muon_b200 as fm
+from flash_muon_b200 import _lib
+from conftest import rel_fro
+from inputs import SYRK_CASES, syrk_input
+from oracle import muon_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = {torch.float32: 1e-5, torch.bfloat16: 1e-2, torch.float16: 1e-2}  # north-star tolerances
+
+
+def check_syrk(x, y):
+    assert not torch.isnan(y).any()
+    assert torch.equal(y, y.T), "upper and lower triangles must be bit-identical mirrors"
+    ref = x.double() @ x.double().T
+    assert rel_fro(y, ref) <= TOL[x.dtype]
+    _lib.device_status()
+
+
+@pytest.mark.parametrize("m,k,dt", SYRK_CASES)
+def test_golden_cases(golden, m, k, dt):
+    x = syrk_input(m, k, dt)
+    y = fm.matmul_transpose(x.to(DEV))
+    check_syrk(x.to(DEV), y)
+    assert rel_fro(y, golden[f"torch_matmul_transpose/{m}x{k}/{dt}"]) <= TOL[dt]
+    assert rel_fro(y, O.matmul_transpose(x)) <= TOL[dt]
+    if dt == torch.float32:
+        assert rel_fro(y, golden["mmt_kernel_interpreter/96x80/torch.float32"]) <= 1e-5
+
+
+def test_config0_fp32_1024():
+    """configs[0]: X 1024x1024 fp32 N(0,1), seed 0; symmetric and equal to torch.matmul."""
+    x = torch.randn(1024, 1024, generator=torch.Generator().manual_seed(0))
+    y = fm.matmul_transpose(x.to(DEV))
+    assert torch.equal(y, y.T)
+    assert rel_fro(y, torch.matmul(x, x.T)) <= 1e-5
+    assert rel_fro(y, O.matmul_transpose(x)) <= 1e-5
+
+
+@pytest.mark.parametrize("m,k", [(1024, 1024), (2048, 2048), (4096, 4096), (8192, 8192),
+                                 (4096, 16384), (16384, 4096)])
+def test_config2_bf16_sweep(m, k):
+    """configs[2]: bf16, entries N(0,1)/sqrt(k); the tall case is transposed first, as in Muon."""
+    g = torch.Generator(device=DEV).manual_seed(m + k)
+    x = (torch.randn(m, k, device=DEV, generator=g) / k ** 0.5).bfloat16()
+    if m > k:
+        x = x.T  # non-contiguous view: the wrapper makes it contiguous like the reference (:88)
+    y = fm.matmul_transpose(x)
+    assert y.shape == (x.shape[0], x.shape[0])
+    assert torch.equal(y, y.T)
+    ref = torch.matmul(x, x.T)  # cuBLAS, the reference's own baseline (benchmark.py:20-21)
+    assert rel_fro(y, ref) <= 1e-2
+    # size-independent properties: the diagonal holds the squared row norms, and a slice agrees
+    # with the CPU oracle
+    diag = (x.double() ** 2).sum(dim=1)
+    assert torch.allclose(y.diagonal().double(), diag, rtol=1e-2, atol=1e-3)
+    rows = slice(0, 64)
+    blk = (x[rows].float().cpu() @ x.float().cpu().T).bfloat16()
+    assert rel_fro(y[rows], blk) <= 1e-2
+    _lib.device_status()
+
+
+ODD = [(1, 8), (7, 8), (8, 1), (100, 72), (129, 64), (257, 136), (130, 1000), (33, 17), (300, 5),
+       (384, 320), (640, 64), (1000, 520)]
+
+
+@pytest.mark.parametrize("bn", ["128", "256"])
+@pytest.mark.parametrize("m,k", ODD)
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+def test_sizes_off_the_tile_grid(m, k, dt, bn, monkeypatch):
+    monkeypatch.setenv("FM_GEMM_BN", bn)
+    x = torch.randn(m, k, device=DEV, generator=torch.Generator(device=DEV).manual_seed(m * k)).to(dt)
+    y = torch.full((m, m), float("nan"), device=DEV, dtype=dt)  # canary: every element written
+    fm.matmul_transpose_assign(x, y)
+    check_syrk(x, y)
+    assert rel_fro(y, O.matmul_transpose(x.cpu())) <= TOL[dt]
+
+
+def test_strided_output_and_input():
+    x = torch.randn(200, 72, device=DEV).bfloat16()
+    ref = O.matmul_transpose(x.cpu()).to(DEV)
+    big = torch.full((200, 512), float("nan"), device=DEV, dtype=torch.bfloat16)
+    out = big[:, 8:208]                                   # row pitch 512
+    fm.matmul_transpose_assign(x, out)
+    assert rel_fro(out, ref) <= 1e-2 and torch.equal(out, out.T)
+    assert torch.isnan(big[:, :8]).all() and torch.isnan(big[:, 208:]).all()
+    outT = torch.empty(200, 200, device=DEV, dtype=torch.bfloat16).T  # column-major view
+    fm.matmul_transpose_assign(x, outT)
+    assert torch.equal(outT, out)
+    every2 = torch.full((200, 400), float("nan"), device=DEV, dtype=torch.bfloat16)[:, ::2]
+    fm.matmul_transpose_assign(x, every2)                 # column stride 2
+    assert torch.equal(every2, out)
+    xbig = torch.randn(200, 128, device=DEV).bfloat16()
+    xs = xbig[:, :72]                                     # row pitch 128 > K
+    assert torch.equal(fm.matmul_transpose(xs), fm.matmul_transpose(xs.contiguous()))
+    xt = torch.randn(72, 200, device=DEV).bfloat16().T    # transposed view of a [72, 200] tensor
+    assert torch.equal(fm.matmul_transpose(xt), fm.matmul_transpose(xt.contiguous()))
+    _lib.device_status()
+
+
+def test_run_to_run_determinism():
+    x = torch.randn(1000, 520, device=DEV).bfloat16()
+    assert torch.equal(fm.matmul_transpose(x), fm.matmul_transpose(x))
+
+
+def test_empty_and_degenerate():
+    assert fm.matmul_transpose(torch.empty(0, 16, device=DEV, dtype=torch.bfloat16)).shape == (0, 0)
+    y = fm.matmul_transpose(torch.empty(5, 0, device=DEV, dtype=torch.bfloat16))
+    assert y.shape == (5, 5) and (y == 0).all()
+
+
+def test_assertions_like_reference():
+    x = torch.randn(16, 16, device=DEV).bfloat16()
+    with pytest.raises(AssertionError, match="same data type"):
+        fm.matmul_transpose_assign(x, torch.empty(16, 16, device=DEV))
+    with pytest.raises(AssertionError, match="must be a 2D tensor"):
+        fm.matmul_transpose_assign(x[0], torch.empty(16, 16, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(AssertionError, match="First dimension"):
+        fm.matmul_transpose_assign(x, torch.empty(8, 8, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(AssertionError, match="First dimension"):
+        fm.matmul_transpose_assign(x, torch.empty(16, 8, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(AssertionError, match="must be a CUDA tensor"):
+        fm.matmul_transpose_assign(x, torch.empty(16, 16, dtype=torch.bfloat16))
+
+
+def test_gemm_nt_epilogue_matches_torch_rounding_points():
+    """C = round(round(a*D) + round(acc)) and its transposed copy, as `a*X + B@X` rounds."""
+    lib = _lib.lib
+    for (M, N, K) in ((128, 128, 64), (384, 200, 136), (1024, 2048, 1024)):
+        A = (torch.randn(M, K, device=DEV) / K ** 0.5).bfloat16()
+        B = torch.randn(N, K, device=DEV).bfloat16()
+        D = torch.randn(M, N, device=DEV).bfloat16()
+        C = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        CT = torch.full((N, M), float("nan"), device=DEV, dtype=torch.bfloat16)
+        _lib.check(lib.fm_gemm_nt(A.data_ptr(), K, B.data_ptr(), K, M, N, K, D.data_ptr(), N, 3.4445,
+                                  1.0, C.data_ptr(), N, CT.data_ptr(), M, 0, 0, 0))
+        ref = 3.4445 * D + A @ B.T          # torch: three bf16 results
+        assert torch.equal(CT, C.T)
+        assert rel_fro(C, ref) <= 2e-3
+        assert (C != ref).float().mean().item() < 1e-3
+    _lib.device_status()
