@@ -1,6 +1,6 @@
 """In-tree build of the C-ABI library ``libflash_muon_b200.so`` for sm_100a.
 
-``python -m flash_muon_b200.build`` compiles every ``csrc/*.cu`` with nvcc and links one shared
+``python flash_muon_b200/build.py`` compiles every ``csrc/*.cu`` with nvcc and links one shared
 object next to this file.  No GPU is needed to build (nvcc cross-compiles).
 """
 from __future__ import annotations

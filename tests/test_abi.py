@@ -23,7 +23,10 @@ def test_header_declares_the_hot_path_entry_points():
 
 
 def test_library_builds_in_tree():
-    from flash_muon_b200 import build
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_fm_build", ROOT / "flash_muon_b200" / "build.py")
+    build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(build)
     path = build.build()
     assert path.exists() and path.parent == ROOT / "flash_muon_b200"
 
