@@ -165,11 +165,12 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------- our arm
-def time_syrk(peaks):
-    """matmul_transpose at 8192^2 bf16 on the current device, against cuBLAS x @ x.T interleaved in
-    the same process.  Input + output (268 MB) exceed L2, so no flush is needed between reps."""
+def time_syrk(peaks, dim=SYRK_DIM, reps=30):
+    """matmul_transpose at dim^2 bf16 (8192 by default) on the current device, against cuBLAS
+    x @ x.T interleaved in the same process.  Input + output (268 MB at 8192) exceed L2, so no
+    flush is needed between reps."""
     import flash_muon_b200 as fm
-    m = k = SYRK_DIM
+    m = k = dim
     x = (torch.randn(m, k, device="cuda") / k ** 0.5).bfloat16()
     y = torch.empty(m, m, device="cuda", dtype=torch.bfloat16)
 
@@ -187,16 +188,16 @@ def time_syrk(peaks):
 
     ours, cublas = [], []
     for _ in range(3):  # interleave: clocks drift under load
-        ours.append(timed(lambda: fm.matmul_transpose_assign(x, y), 5, 30))
-        cublas.append(timed(lambda: torch.matmul(x, x.T, out=y), 5, 30))
+        ours.append(timed(lambda: fm.matmul_transpose_assign(x, y), 5, reps))
+        cublas.append(timed(lambda: torch.matmul(x, x.T, out=y), 5, reps))
     t, tc = min(ours), min(cublas)
     alg = m * (m + 1) * k
     tiles = sum(min(2 * j + 2, m // 128) for j in range(m // 256))  # 128x256 tiles issued
     execd = tiles * 2 * 128 * 256 * k
     res = {"shape": [m, k], "ms": t, "tflops_effective": 2 * m * m * k / t / 1e9,
            "tflops_algorithmic": alg / t / 1e9, "tflops_executed": execd / t / 1e9,
-           "cublas_ms": tc, "speedup_vs_cublas": tc / t, "reps": 30}
-    roof = {"kernel": "gemm_tc_kernel<bf16,256> as matmul_transpose 8192x8192", "bound": "tensor",
+           "cublas_ms": tc, "speedup_vs_cublas": tc / t, "reps": reps}
+    roof = {"kernel": f"gemm_tc_kernel<bf16,256> as matmul_transpose {m}x{k}", "bound": "tensor",
             "achieved": alg / t / 1e9, "peak": peaks["bf16"], "unit": "TFLOP/s",
             "frac": alg / t / 1e9 / peaks["bf16"], "frac_executed": execd / t / 1e9 / peaks["bf16"],
             "traffic": None, "peak_source": f"{peaks['source']} burst (kernel timed alone)"}
@@ -216,7 +217,12 @@ def run_ours(args):
         dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=dev)
     peaks = measured_peaks()
 
-    shapes = LLAMA_LAYER * N_LAYERS
+    if args.syrk_only:  # profiling aid: only the matmul_transpose leg
+        mt, roof = time_syrk(peaks, args.syrk_dim, args.reps)
+        print(json.dumps({"matmul_transpose": mt, "roofline": roof}), flush=True)
+        return
+
+    shapes = LLAMA_LAYER * args.layers
     g = torch.Generator(device=dev).manual_seed(0)  # same values on every rank (DP replicas)
     params = [torch.nn.Parameter((torch.randn(*s, device=dev, generator=g) * 0.02).bfloat16())
               for s in shapes]
@@ -250,6 +256,14 @@ def run_ours(args):
     ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     clocks = clk.summary()
     fm._lib.device_status()
+
+    if args.skip_extras:  # profiling aid: the device-resident leg only
+        if rank == 0:
+            print(json.dumps({"metric": "muon_step_ms", "value": ms, "layers": args.layers,
+                              "note": "profiling run, not a bench line"}), flush=True)
+        if ws > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- end-to-end leg: gradients arrive from pinned host memory, owned parameters go back
     # ownership is per numel group: rank r owns params[base + r] of every round
@@ -285,13 +299,14 @@ def run_ours(args):
     rounds = sum((len(grp["params"]) + ws - 1) // ws for grp in opt.param_groups)
     launches_per_step = len(owned) * (1 + 2 + 3 * HP["ns_steps"]) + rounds
     alg, full = full_step_flops()
+    alg, full = alg * args.layers / N_LAYERS, full * args.layers / N_LAYERS
 
     line = {
         "metric": "muon_step_ms", "value": ms, "unit": "ms", "n_gpus": ws, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "Muon.step on Llama-3-8B-shaped matrices (BASELINE configs[4])",
-                   "matrices": len(shapes), "elements": sum(a * b for a, b in shapes),
+                   "layers": args.layers, "matrices": len(shapes), "elements": sum(a * b for a, b in shapes),
                    "ns_steps": HP["ns_steps"], "parallelism": f"dp{ws} round-robin ownership",
                    "l2": "working set (42+ GB) far larger than L2; no flush needed"},
         "step_tflops_algorithmic": alg / ms / 1e9, "step_tflops_cublas_equivalent": full / ms / 1e9,
@@ -327,6 +342,12 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    # profiling aids (the defaults are the benchmark):
+    ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers of the matrix set (32 = the config)")
+    ap.add_argument("--skip-extras", action="store_true", help="device-resident leg only")
+    ap.add_argument("--syrk-only", action="store_true", help="only the matmul_transpose leg")
+    ap.add_argument("--syrk-dim", type=int, default=SYRK_DIM)
+    ap.add_argument("--reps", type=int, default=30)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

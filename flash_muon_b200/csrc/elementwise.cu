@@ -124,6 +124,61 @@ scale_transpose_kernel(const T* __restrict__ g, long long rows, long long cols, 
   }
 }
 
+
+// Fast path of the kernel above for matrices whose rows and columns are multiples of 64 and whose
+// pointers and pitches allow 16-byte accesses: every global access is a full 16-byte vector, both
+// outputs are written as whole 128-byte row segments.
+template <typename T>
+__global__ void __launch_bounds__(256)
+scale_transpose_vec_kernel(const T* __restrict__ g, long long rows, long long cols, long long ldg,
+                           const float* __restrict__ partials, int nparts,
+                           __nv_bfloat16* __restrict__ xd, long long ldxd,
+                           __nv_bfloat16* __restrict__ xt, long long ldxt) {
+  constexpr int V = 16 / sizeof(T);        // input elements per 16-byte load
+  constexpr int CHUNKS = 64 / V;           // loads per tile row
+  __shared__ float red[8];
+  // 8-element column groups are XOR-swizzled with the row group, so that both the row-wise
+  // 16-byte stores and the column-wise gathers below are free of bank conflicts
+  __shared__ __align__(16) __nv_bfloat16 tile[64][64];
+  auto swz = [](int r, int c) { return (((c >> 3) ^ ((r >> 3) & 7)) << 3) | (c & 7); };
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += 256) s += partials[i];
+  const float total = block_sum_256(s, red);
+  const float d = __bfloat162float(__float2bfloat16_rn(sqrtf(total)));
+  const float dp = __bfloat162float(__float2bfloat16_rn(d + 1e-7f));
+
+  const long long tiles_c = cols / 64;
+  const long long tr = blockIdx.x / tiles_c, tc = blockIdx.x - tr * tiles_c;
+  const long long r0 = tr * 64, c0 = tc * 64;
+#pragma unroll
+  for (int i = 0; i < (64 * CHUNKS) / 256; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    const int rr = idx / CHUNKS, cc = (idx % CHUNKS) * V;
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(g + (r0 + rr) * ldg + c0 + cc));
+    const T* e = reinterpret_cast<const T*>(&raw);
+    alignas(16) __nv_bfloat16 q[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) q[j] = __float2bfloat16_rn(as_bf16_value<T>(e[j]) / dp);
+    if (xd != nullptr) {
+      if (V == 8) *reinterpret_cast<uint4*>(xd + (r0 + rr) * ldxd + c0 + cc) = *reinterpret_cast<uint4*>(q);
+      else *reinterpret_cast<uint2*>(xd + (r0 + rr) * ldxd + c0 + cc) = *reinterpret_cast<uint2*>(q);
+    }
+    if (V == 8) *reinterpret_cast<uint4*>(&tile[rr][swz(rr, cc)]) = *reinterpret_cast<uint4*>(q);
+    else *reinterpret_cast<uint2*>(&tile[rr][swz(rr, cc)]) = *reinterpret_cast<uint2*>(q);
+  }
+  if (xt == nullptr) return;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int idx = threadIdx.x + i * 256;   // 64 output rows x 8 chunks of 8 elements
+    const int cc = idx >> 3, rs = (idx & 7) * 8;
+    alignas(16) __nv_bfloat16 q[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) q[e] = tile[rs + e][swz(rs + e, cc)];
+    *reinterpret_cast<uint4*>(xt + (c0 + cc) * ldxt + r0 + rs) = *reinterpret_cast<uint4*>(q);
+  }
+}
+
 // ---------------------------------------------------------------- momentum + Nesterov
 // torch's lerp (element kernel in fp32): w < 0.5 ? a + w*(b-a) : b - (b-a)*(1-w)
 __device__ __forceinline__ float lerp_f(float a, float b, float w) {
@@ -249,8 +304,16 @@ int normalize_t(const T* g, long long rows, long long cols, long long ldg, __nv_
   FM_CUDA_CHECK(cudaGetLastError());
   const long long tiles = ((rows + 63) / 64) * ((cols + 63) / 64);
   if (tiles > 0x7fffffffLL) return fail(FM_ERR_UNSUPPORTED, "matrix too large");
-  scale_transpose_kernel<T><<<(int)tiles, 256, 0, stream>>>(g, rows, cols, ldg, partials, (int)nb,
-                                                            xd, ldxd, xt, ldxt);
+  const bool fast = (rows % 64 == 0) && (cols % 64 == 0) && (ldg % V == 0) &&
+                    ((reinterpret_cast<uintptr_t>(g) & 15u) == 0) &&
+                    (xd == nullptr || (ldxd % 8 == 0 && (reinterpret_cast<uintptr_t>(xd) & 15u) == 0)) &&
+                    (xt == nullptr || (ldxt % 8 == 0 && (reinterpret_cast<uintptr_t>(xt) & 15u) == 0));
+  if (fast)
+    scale_transpose_vec_kernel<T><<<(int)tiles, 256, 0, stream>>>(g, rows, cols, ldg, partials,
+                                                                  (int)nb, xd, ldxd, xt, ldxt);
+  else
+    scale_transpose_kernel<T><<<(int)tiles, 256, 0, stream>>>(g, rows, cols, ldg, partials, (int)nb,
+                                                              xd, ldxd, xt, ldxt);
   FM_CUDA_CHECK(cudaGetLastError());
   return FM_OK;
 }

@@ -1,0 +1,149 @@
+// Pieces shared by the single-CTA and the CTA-pair tensor-core GEMM kernels: kernel parameters,
+// numeric traits and the register epilogue (addend load, rounding-faithful arithmetic, direct and
+// transposed global stores with the mirror rule of the symmetric product).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+
+namespace fm {
+
+struct GemmParams {
+  int M, N, K;
+  int sym;        // 1: triangular schedule + mirrored store (requires A == B, M == N)
+  int tiles_m;    // row tiles of the schedule
+  int num_tiles;  // length of the static tile list
+  int num_kb;     // ceil(K / 64)
+  const void* D;  // optional addend, row-major, unit column stride
+  long long ldd;
+  void* C;        // direct output (may be null): C[r*ldc_r + c*ldc_c]
+  long long ldc_r, ldc_c;
+  void* CT;       // transposed output (may be null): element (r,c) goes to CT[c*ldt_r + r*ldt_c]
+  long long ldt_r, ldt_c;
+  float alpha, beta;
+  int precise;    // 1: single rounding of alpha*D + beta*acc
+  int d_vec;      // D rows can be read with 16-byte loads
+  int c_vec;      // C rows can be written with 16-byte stores
+  int t_pack;     // CT can be written as pairs of adjacent rows (4-byte stores)
+  unsigned int* err;
+};
+
+template <typename T>
+struct Num;
+template <>
+struct Num<__nv_bfloat16> {
+  static constexpr uint32_t kFormat = 1;
+  static __device__ __forceinline__ __nv_bfloat16 rn(float f) { return __float2bfloat16_rn(f); }
+  static __device__ __forceinline__ float f(__nv_bfloat16 v) { return __bfloat162float(v); }
+};
+template <>
+struct Num<__half> {
+  static constexpr uint32_t kFormat = 0;
+  static __device__ __forceinline__ __half rn(float f) { return __float2half_rn(f); }
+  static __device__ __forceinline__ float f(__half v) { return __half2float(v); }
+};
+
+// Addend values D[row][c0 .. c0+31] of one epilogue chunk (zeros outside the matrix).
+template <typename T>
+__device__ __forceinline__ void epilogue_load_d(const GemmParams& p, int row, int c0, T (&dv)[32]) {
+  const T* Dp = reinterpret_cast<const T*>(p.D);
+  if (Dp == nullptr) return;
+  if (row < p.M && c0 < p.N) {
+    const T* dptr = Dp + (long long)row * p.ldd + c0;
+    if (p.d_vec && c0 + 32 <= p.N) {
+      const uint4* d4 = reinterpret_cast<const uint4*>(dptr);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dv)[v] = __ldg(d4 + v);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) dv[j] = (c0 + j < p.N) ? dptr[j] : Num<T>::rn(0.f);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dv[j] = Num<T>::rn(0.f);
+  }
+}
+
+// One 32-column chunk of one accumulator row: arithmetic + stores.
+//   raw : fp32 accumulator bits of columns c0..c0+31 of `row`
+//   bi  : index of the 128-row block `row` belongs to (diagonal test of the symmetric product)
+// Symmetric mode: a 128-column block left of the diagonal block is skipped (its mirror image is
+// produced by the block above the diagonal); inside the diagonal block only c >= row is stored
+// and c > row mirrored, so both triangles come from the same rounded registers.
+template <typename T>
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, const uint32_t (&raw)[32],
+                                               const T (&dv)[32], int row, int c0, int bi) {
+  if (c0 >= p.N) return;  // warp-uniform
+  const int cb = c0 >> 7;
+  if (p.sym && cb < bi) return;  // warp-uniform
+  const bool diag = p.sym && (cb == bi);
+  const bool full_cols = (c0 + 32 <= p.N);
+  const bool row_ok = row < p.M;
+  T* const Cp = reinterpret_cast<T*>(p.C);
+  T* const CTp = reinterpret_cast<T*>(p.CT);
+
+  alignas(16) T outv[32];
+  if (p.D != nullptr) {
+    if (p.precise) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        outv[j] = Num<T>::rn(fmaf(p.alpha, Num<T>::f(dv[j]), p.beta * __uint_as_float(raw[j])));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const T tacc = Num<T>::rn(__uint_as_float(raw[j]));
+        const T u = Num<T>::rn(p.alpha * Num<T>::f(dv[j]));
+        const T w = Num<T>::rn(p.beta * Num<T>::f(tacc));
+        outv[j] = Num<T>::rn(Num<T>::f(u) + Num<T>::f(w));
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) outv[j] = Num<T>::rn(__uint_as_float(raw[j]));
+  }
+
+  if (Cp != nullptr && row_ok) {
+    if (p.c_vec && full_cols && !diag) {
+      uint4* c4 = reinterpret_cast<uint4*>(Cp + (long long)row * p.ldc_r + c0);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) c4[v] = reinterpret_cast<const uint4*>(outv)[v];
+    } else {
+      T* cptr = Cp + (long long)row * p.ldc_r + (long long)c0 * p.ldc_c;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int c = c0 + j;
+        if (c < p.N && (!diag || c >= row)) cptr[(long long)j * p.ldc_c] = outv[j];
+      }
+    }
+  }
+  if (CTp != nullptr) {
+    // the 32 rows of this warp start at a multiple of 32: all of them in range <=> last one is
+    const bool warp_rows_ok = ((row | 31) < p.M);
+    if (p.t_pack && full_cols && !diag && warp_rows_ok) {
+      // Lanes 2u and 2u+1 hold adjacent rows.  Exchange packed column pairs so that the even
+      // lane writes rows (2u, 2u+1) of the even columns and the odd lane those of the odd
+      // columns: 16 four-byte stores per lane instead of 32 two-byte stores.
+      const uint32_t* own = reinterpret_cast<const uint32_t*>(outv);
+      const bool odd = (row & 1) != 0;
+      T* tbase = CTp + (long long)c0 * p.ldt_r + (row & ~1);
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        const uint32_t mine = own[jj];
+        const uint32_t theirs = __shfl_xor_sync(0xffffffffu, mine, 1);
+        // even lane: {own[2jj], partner[2jj]}; odd lane: {partner[2jj+1], own[2jj+1]}
+        const uint32_t v = odd ? __byte_perm(theirs, mine, 0x7632) : __byte_perm(mine, theirs, 0x5410);
+        const int j = 2 * jj + (odd ? 1 : 0);
+        *reinterpret_cast<uint32_t*>(tbase + (long long)j * p.ldt_r) = v;
+      }
+    } else if (row_ok) {
+      T* tptr = CTp + (long long)c0 * p.ldt_r + (long long)row * p.ldt_c;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int c = c0 + j;
+        if (c < p.N && (!diag || c > row)) tptr[(long long)j * p.ldt_r] = outv[j];
+      }
+    }
+  }
+}
+
+}  // namespace fm

@@ -20,6 +20,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "gemm_common.cuh"
 #include "gemm_tc.cuh"
 #include "ptx.cuh"
 
@@ -32,25 +33,6 @@ constexpr int BK = 64;           // K extent of one smem stage: 64 x 2 B = one 1
 constexpr int UMMA_K = 16;       // K of one tcgen05.mma for 16-bit operands
 constexpr int kThreads = 192;
 constexpr int kSlabBytes = 128 * BK * 2;  // one 128-row operand slab = one TMA box (16 KiB)
-
-struct GemmParams {
-  int M, N, K;
-  int sym;        // 1: triangular schedule + mirrored store (requires A == B, M == N)
-  int tiles_m;    // ceil(M / 128)
-  int num_tiles;  // length of the static tile list
-  int num_kb;     // ceil(K / 64)
-  const void* D;  // optional addend, row-major, unit column stride
-  long long ldd;
-  void* C;        // direct output (may be null): C[r*ldc_r + c*ldc_c]
-  long long ldc_r, ldc_c;
-  void* CT;       // transposed output (may be null): element (r,c) goes to CT[c*ldt_r + r*ldt_c]
-  long long ldt_r, ldt_c;
-  float alpha, beta;
-  int precise;    // 1: single rounding of alpha*D + beta*acc
-  int d_vec;      // D rows can be read with 16-byte loads
-  int c_vec;      // C rows can be written with 16-byte stores
-  unsigned int* err;
-};
 
 template <int BN>
 struct Cfg {
@@ -105,21 +87,6 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, int t) {
   if (left <= 128 && o.ncols > 128) o.ncols = 128;
   return o;
 }
-
-template <typename T>
-struct Num;
-template <>
-struct Num<__nv_bfloat16> {
-  static constexpr uint32_t kFormat = 1;
-  static __device__ __forceinline__ __nv_bfloat16 rn(float f) { return __float2bfloat16_rn(f); }
-  static __device__ __forceinline__ float f(__nv_bfloat16 v) { return __bfloat162float(v); }
-};
-template <>
-struct Num<__half> {
-  static constexpr uint32_t kFormat = 0;
-  static __device__ __forceinline__ __half rn(float f) { return __float2half_rn(f); }
-  static __device__ __forceinline__ float f(__half v) { return __half2float(v); }
-};
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -229,84 +196,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_ph = 0;
-    T* const Cp = reinterpret_cast<T*>(p.C);
-    T* const CTp = reinterpret_cast<T*>(p.CT);
-    const T* const Dp = reinterpret_cast<const T*>(p.D);
     for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
       const Tile tl = decode_tile<BN>(p, t);
+      const int row = tl.m0 + q * 32 + lane;
+      const int nchunks = tl.ncols >> 5;
+      // the addend does not depend on the accumulator: fetch the first chunk before waiting
+      alignas(16) T dcur[32], dnext[32];
+      epilogue_load_d<T>(p, row, tl.n0, dcur);
       bool ok = ptx::mbar_wait(tfull_bar(acc), acc_ph, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after();
-      const int row = tl.m0 + q * 32 + lane;
-      const bool row_ok = row < p.M;
-      const int nchunks = tl.ncols >> 5;
       for (int ch = 0; ch < nchunks; ++ch) {
         uint32_t raw[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + ch * 32),
                            raw);
+        if (ch + 1 < nchunks) epilogue_load_d<T>(p, row, tl.n0 + (ch + 1) * 32, dnext);
         ptx::tmem_ld_wait();
-        const int c0 = tl.n0 + ch * 32;
-        if (c0 >= p.N) continue;  // warp-uniform
-        const bool full_cols = (c0 + 32 <= p.N);
-        const bool diag = p.sym && ((c0 >> 7) == tl.bi);
-        alignas(16) T outv[32];
-        if (Dp != nullptr) {
-          alignas(16) T dv[32];
-          if (row_ok) {
-            const T* dptr = Dp + (long long)row * p.ldd + c0;
-            if (p.d_vec && full_cols) {
-              const uint4* d4 = reinterpret_cast<const uint4*>(dptr);
+        epilogue_store<T>(p, raw, dcur, row, tl.n0 + ch * 32, tl.bi);
+        if (p.D != nullptr) {
 #pragma unroll
-              for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dv)[v] = __ldg(d4 + v);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) dv[j] = (c0 + j < p.N) ? dptr[j] : Num<T>::rn(0.f);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) dv[j] = Num<T>::rn(0.f);
-          }
-          if (p.precise) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              outv[j] = Num<T>::rn(fmaf(p.alpha, Num<T>::f(dv[j]), p.beta * __uint_as_float(raw[j])));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const T tacc = Num<T>::rn(__uint_as_float(raw[j]));
-              const T u = Num<T>::rn(p.alpha * Num<T>::f(dv[j]));
-              const T w = Num<T>::rn(p.beta * Num<T>::f(tacc));
-              outv[j] = Num<T>::rn(Num<T>::f(u) + Num<T>::f(w));
-            }
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) outv[j] = Num<T>::rn(__uint_as_float(raw[j]));
-        }
-        if (row_ok) {
-          if (Cp != nullptr) {
-            if (p.c_vec && full_cols && !diag) {
-              uint4* c4 = reinterpret_cast<uint4*>(Cp + (long long)row * p.ldc_r + c0);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) c4[v] = reinterpret_cast<const uint4*>(outv)[v];
-            } else {
-              T* cptr = Cp + (long long)row * p.ldc_r + (long long)c0 * p.ldc_c;
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int c = c0 + j;
-                if (c < p.N && (!diag || c >= row)) cptr[(long long)j * p.ldc_c] = outv[j];
-              }
-            }
-          }
-          if (CTp != nullptr) {
-            T* tptr = CTp + (long long)c0 * p.ldt_r + (long long)row * p.ldt_c;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int c = c0 + j;
-              if (c < p.N && (!diag || c > row)) tptr[(long long)j * p.ldt_r] = outv[j];
-            }
-          }
+          for (int v = 0; v < 4; ++v)
+            reinterpret_cast<uint4*>(dcur)[v] = reinterpret_cast<const uint4*>(dnext)[v];
         }
       }
       ptx::tc_fence_before();
@@ -393,8 +304,24 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   p.d_vec = (a.D != nullptr) && ((reinterpret_cast<uintptr_t>(a.D) & 15u) == 0) && (a.ldd % 8 == 0);
   p.c_vec = (a.C != nullptr) && ((reinterpret_cast<uintptr_t>(a.C) & 15u) == 0) &&
             (a.ldc_c == 1) && (a.ldc_r % 8 == 0);
+  p.t_pack = (a.CT != nullptr) && (a.ldt_c == 1) && (a.ldt_r % 2 == 0) &&
+             ((reinterpret_cast<uintptr_t>(a.CT) & 3u) == 0);
   p.err = device_error_word();
   if (!p.err) return fail(FM_ERR_CUDA, "no current CUDA device");
+
+  // CTA pairs on 256 x 256 tiles when there are enough tiles to occupy most of the pairs;
+  // otherwise single CTAs on 128 x 256 or 128 x 128 tiles (more, smaller units of work).
+  int impl = 1;
+  {
+    const int tiles2 = gemm_tc2_tiles(a.M, a.N, a.sym);
+    const int pairs = gemm_tc2_max_pairs(a.dtype);
+    if (pairs > 0 && tiles2 * 10 >= pairs * 6) impl = 2;
+    if (const char* e = getenv("FM_GEMM_IMPL")) {
+      const int v = atoi(e);
+      if (v == 1 || (v == 2 && pairs > 0)) impl = v;
+    }
+  }
+  if (impl == 2) return gemm_tc2_launch(a.dtype, tmA, tmB, p, stream);
 
   // Tile width: 256 columns (less operand traffic per FLOP) unless that leaves most SMs idle.
   int bn = 256;

@@ -1,5 +1,6 @@
 // Internal interface of the tcgen05 GEMM family (see gemm_tc.cu).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
 
@@ -25,6 +26,13 @@ struct GemmArgs {
 
 // Validates, encodes the tensor maps and enqueues the kernel on `stream`.
 int gemm_tc(const GemmArgs& args, cudaStream_t stream);
+
+// CTA-pair (cluster of two) variant on 256 x 256 tiles, gemm_tc2.cu.
+struct GemmParams;
+int gemm_tc2_tiles(int64_t M, int64_t N, int sym);
+int gemm_tc2_max_pairs(int dtype);
+int gemm_tc2_launch(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
+                    cudaStream_t stream);
 
 // Exact-fp32 FFMA symmetric rank-k update for f32 inputs and layouts TMA cannot address.
 int syrk_simt(const void* x, void* y, int64_t M, int64_t K, int64_t ldx, int64_t ldy_row,

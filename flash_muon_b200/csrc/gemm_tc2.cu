@@ -1,0 +1,280 @@
+// CTA-pair variant of the tensor-core GEMM family (see gemm_tc.cu for the operation itself):
+// two CTAs of a cluster compute one 256 x 256 output tile with tcgen05.mma.cta_group::2.
+// Each CTA stages only its own 128 rows of A and its own 128 rows of B per 64-wide K slab
+// (32 KiB per stage instead of 48 KiB), so the operand traffic per FLOP from L2 and from shared
+// memory drops by a third and a half respectively against the 128 x 256 single-CTA tile, and six
+// stages fit.  No load is a multicast: the two CTAs issue plain TMA tile loads into their own
+// shared memory; only the completion bytes are counted on the leader's mbarrier, and the MMA
+// completion is signalled to both CTAs by tcgen05.commit.
+//
+// Roles per CTA (192 threads): warp 0 TMA producer (both CTAs), warp 1 MMA issuer (leader CTA
+// only; both CTAs take part in the TMEM allocation), warps 2..5 epilogue (both CTAs, each for
+// its own 128 accumulator rows).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "gemm_common.cuh"
+#include "gemm_tc.cuh"
+#include "ptx.cuh"
+
+namespace fm {
+namespace {
+
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kSlabBytes = 128 * BK * 2;      // 16 KiB: 128 rows x 64 columns of 16-bit values
+constexpr int kStages = 6;
+constexpr int kStageBytes = 2 * kSlabBytes;   // this CTA's A slab + B slab
+constexpr int kTmemCols = 512;                // two accumulators of 256 fp32 columns
+constexpr int kNumBars = 2 * kStages + 4;
+constexpr int kSmemBytes = kStages * kStageBytes + kNumBars * 8 + 16 + 1024;
+
+struct Tile2 {
+  int m0, n0;  // first row / column of the 256 x 256 tile
+};
+
+__device__ __forceinline__ Tile2 decode_tile2(const GemmParams& p, int t) {
+  Tile2 o;
+  if (!p.sym) {
+    const int tn = t / p.tiles_m;
+    const int tm = t - tn * p.tiles_m;
+    o.m0 = tm * 256;
+    o.n0 = tn * 256;
+  } else {
+    int j = (int)((sqrtf(8.f * (float)t + 1.f) - 1.f) * 0.5f);
+    while ((long long)(j + 1) * (j + 2) / 2 <= t) ++j;
+    while ((long long)j * (j + 1) / 2 > t) --j;
+    const int i = t - j * (j + 1) / 2;
+    o.m0 = i * 256;
+    o.n0 = j * 256;
+  }
+  return o;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint32_t bar_base = smem_base + kStages * kStageBytes;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kStages * kStageBytes + kNumBars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  auto a_smem = [&](int s) { return smem_base + s * kStageBytes; };
+  auto b_smem = [&](int s) { return smem_base + s * kStageBytes + kSlabBytes; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();  // 0 = leader (issues the MMAs)
+  const int pair = blockIdx.x >> 1;
+  const int npairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);   // leader's producer arrives once (with the byte count)
+      ptx::mbar_init(empty_bar(s), 1);  // one commit arrival per use
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 8);  // 4 epilogue warps of each of the two CTAs
+    }
+    *abort_flag = 0;
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&tmA);
+    ptx::prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();  // the peer's barriers exist before anything remote touches them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = pair; ok && t < p.num_tiles; t += npairs) {
+        const Tile2 tl = decode_tile2(p, t);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t leader_full = ptx::mapa(full_bar(s), 0);
+          if (rank == 0) ptx::mbar_expect_tx(full_bar(s), 4u * kSlabBytes);  // both CTAs' slabs
+          ptx::tma_load_2d_pair(a_smem(s), &tmA, leader_full, kb * BK, tl.m0 + (int)rank * 128);
+          ptx::tma_load_2d_pair(b_smem(s), &tmB, leader_full, kb * BK, tl.n0 + (int)rank * 128);
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      const uint32_t idesc = ptx::make_idesc_f16(Num<T>::kFormat, 256, 256);
+      for (int t = pair; ok && t < p.num_tiles; t += npairs) {
+        if (!ptx::mbar_wait_cluster(tempty_bar(acc), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_smem(s));
+          const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_smem(s));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            ptx::umma_f16_pair(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
+                               (uint32_t)((kb | k) != 0));
+          ptx::umma_commit_pair(empty_bar(s), 0x3);  // frees the stage in both CTAs
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::umma_commit_pair(tfull_bar(acc), 0x3);  // accumulator halves complete in both CTAs
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------- epilogue (both CTAs)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int t = pair; t < p.num_tiles; t += npairs) {
+      const Tile2 tl = decode_tile2(p, t);
+      const int row = tl.m0 + (int)rank * 128 + q * 32 + lane;
+      const int bi = (tl.m0 >> 7) + (int)rank;
+      alignas(16) T dcur[32], dnext[32];
+      epilogue_load_d<T>(p, row, tl.n0, dcur);
+      bool ok = ptx::mbar_wait(tfull_bar(acc), acc_ph, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after();
+#pragma unroll 1
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t raw[32];
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 256 + ch * 32),
+                           raw);
+        if (ch + 1 < 8) epilogue_load_d<T>(p, row, tl.n0 + (ch + 1) * 32, dnext);
+        ptx::tmem_ld_wait();
+        epilogue_store<T>(p, raw, dcur, row, tl.n0 + ch * 32, bi);
+        if (p.D != nullptr) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            reinterpret_cast<uint4*>(dcur)[v] = reinterpret_cast<const uint4*>(dnext)[v];
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0));
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1u;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();  // neither CTA frees TMEM or exits while the other may still use it
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 0x47320000u | (unsigned)blockIdx.x);
+}
+
+template <typename T>
+int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int max_pairs,
+            cudaStream_t stream) {
+  const int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T>, tmA, tmB, p));
+  return FM_OK;
+}
+
+// Clusters of two CTAs that can be resident at once on the current device (0 if unknown).
+template <typename T>
+int max_pairs_for() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    if (cudaFuncSetAttribute(gemm_tc2_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBytes) != cudaSuccess)
+      return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<T>, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace
+
+int gemm_tc2_tiles(int64_t M, int64_t N, int sym) {
+  const int64_t tm = (M + 255) / 256, tn = (N + 255) / 256;
+  return (int)(sym ? tn * (tn + 1) / 2 : tm * tn);
+}
+
+int gemm_tc2_max_pairs(int dtype) {
+  return dtype == FM_BF16 ? max_pairs_for<__nv_bfloat16>() : max_pairs_for<__half>();
+}
+
+// `p` arrives filled except for the schedule fields, which depend on the tile shape.
+int gemm_tc2_launch(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
+                    cudaStream_t stream) {
+  p.tiles_m = (p.M + 255) / 256;
+  p.num_tiles = gemm_tc2_tiles(p.M, p.N, p.sym);
+  const int max_pairs = gemm_tc2_max_pairs(dtype);
+  if (max_pairs <= 0) return fail(FM_ERR_CUDA, "no resident CTA pair possible for the GEMM kernel");
+  return dtype == FM_BF16 ? launch2<__nv_bfloat16>(tmA, tmB, p, max_pairs, stream)
+                          : launch2<__half>(tmA, tmB, p, max_pairs, stream);
+}
+
+}  // namespace fm
