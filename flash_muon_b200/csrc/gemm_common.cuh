@@ -26,7 +26,23 @@ struct GemmParams {
   int c_vec;      // C rows can be written with 16-byte stores
   int t_pack;     // CT can be written as pairs of adjacent rows (4-byte stores)
   unsigned int* err;
+#ifdef FM_TRACE
+  unsigned long long* trace;  // diagnostic builds only: 8 timestamps per CTA
+#endif
 };
+
+#ifdef FM_TRACE
+__device__ __forceinline__ void trace_mark(const GemmParams& p, int slot) {
+  if (p.trace != nullptr) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.trace[(size_t)blockIdx.x * 8 + slot] = t;
+  }
+}
+#define FM_TRACE_MARK(p, slot) ::fm::trace_mark(p, slot)
+#else
+#define FM_TRACE_MARK(p, slot) ((void)0)
+#endif
 
 template <typename T>
 struct Num;
@@ -68,15 +84,23 @@ __device__ __forceinline__ void epilogue_load_d(const GemmParams& p, int row, in
 //   raw : fp32 accumulator bits of columns c0..c0+31 of `row`
 //   bi  : index of the 128-row block `row` belongs to (diagonal test of the symmetric product)
 // Symmetric mode: a 128-column block left of the diagonal block is skipped (its mirror image is
-// produced by the block above the diagonal); inside the diagonal block only c >= row is stored
-// and c > row mirrored, so both triangles come from the same rounded registers.
+// produced by the block above the diagonal); on the diagonal only c >= row is stored and
+// c > row mirrored, so both triangles come from the same rounded registers.
 template <typename T>
 __device__ __forceinline__ void epilogue_store(const GemmParams& p, const uint32_t (&raw)[32],
                                                const T (&dv)[32], int row, int c0, int bi) {
   if (c0 >= p.N) return;  // warp-uniform
   const int cb = c0 >> 7;
   if (p.sym && cb < bi) return;  // warp-uniform
-  const bool diag = p.sym && (cb == bi);
+  // Inside the diagonal 128 x 128 block the warp's 32 rows meet this chunk's 32 columns in one
+  // of three ways: wholly below the diagonal (nothing to store), wholly above (same as any
+  // other block) or on it (element-wise rule).  All three tests are warp-uniform.
+  bool diag = false;
+  if (p.sym && cb == bi) {
+    const int r_first = row & ~31;
+    if (c0 + 31 < r_first) return;
+    diag = (c0 < r_first + 32);
+  }
   const bool full_cols = (c0 + 32 <= p.N);
   const bool row_ok = row < p.M;
   T* const Cp = reinterpret_cast<T*>(p.C);

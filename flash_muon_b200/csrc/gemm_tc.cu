@@ -110,6 +110,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) FM_TRACE_MARK(p, 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -133,6 +134,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) FM_TRACE_MARK(p, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
@@ -150,6 +152,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int q = 0; q < nb; ++q)
             ptx::tma_load_2d(b_smem(s) + q * kSlabBytes, &tmB, full_bar(s), kb * BK,
                              tl.n0 + q * 128);
+          if (t == (int)blockIdx.x && kb == 0) FM_TRACE_MARK(p, 2);
           if (++s == C::kStages) { s = 0; ph ^= 1u; }
         }
       }
@@ -171,6 +174,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t idesc = ptx::make_idesc_f16(Num<T>::kFormat, BM, (uint32_t)tl.ncols);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          if (kb == 0) FM_TRACE_MARK(p, 3);
           ptx::tc_fence_after();
           const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_smem(s));
           const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_smem(s));
@@ -185,6 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (++s == C::kStages) { s = 0; ph ^= 1u; }
         }
         if (!ok) break;
+        FM_TRACE_MARK(p, 4);
         ptx::umma_commit(tfull_bar(acc));  // accumulator complete
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
@@ -206,6 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = ptx::mbar_wait(tfull_bar(acc), acc_ph, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (threadIdx.x == 64) FM_TRACE_MARK(p, 5);
       ptx::tc_fence_after();
       for (int ch = 0; ch < nchunks; ++ch) {
         uint32_t raw[32];
@@ -220,6 +226,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             reinterpret_cast<uint4*>(dcur)[v] = reinterpret_cast<const uint4*>(dnext)[v];
         }
       }
+      if (threadIdx.x == 64) FM_TRACE_MARK(p, 6);
       ptx::tc_fence_before();
       ptx::mbar_arrive(tempty_bar(acc));
       acc ^= 1;
@@ -239,6 +246,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   }
+  if (threadIdx.x == 0) FM_TRACE_MARK(p, 7);
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 0x47450000u | (unsigned)blockIdx.x);
 }
 
@@ -275,6 +283,11 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaSt
 
 }  // namespace
 
+#ifdef FM_TRACE
+static unsigned long long* g_trace_ptr = nullptr;
+extern "C" void fm_debug_set_trace(void* ptr) { g_trace_ptr = static_cast<unsigned long long*>(ptr); }
+#endif
+
 int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   if (a.dtype != FM_BF16 && a.dtype != FM_F16)
     return fail(FM_ERR_UNSUPPORTED, "tensor-core GEMM covers bf16 and f16 only");
@@ -307,6 +320,9 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   p.t_pack = (a.CT != nullptr) && (a.ldt_c == 1) && (a.ldt_r % 2 == 0) &&
              ((reinterpret_cast<uintptr_t>(a.CT) & 3u) == 0);
   p.err = device_error_word();
+#ifdef FM_TRACE
+  p.trace = g_trace_ptr;
+#endif
   if (!p.err) return fail(FM_ERR_CUDA, "no current CUDA device");
 
   // CTA pairs on 256 x 256 tiles when there are enough tiles to occupy most of the pairs;

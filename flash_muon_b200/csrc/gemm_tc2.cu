@@ -74,6 +74,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) FM_TRACE_MARK(p, 0);
   const uint32_t rank = ptx::cluster_ctarank();  // 0 = leader (issues the MMAs)
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
@@ -101,6 +102,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   ptx::cluster_sync();  // the peer's barriers exist before anything remote touches them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) FM_TRACE_MARK(p, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer (both CTAs)
@@ -116,6 +118,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (rank == 0) ptx::mbar_expect_tx(full_bar(s), 4u * kSlabBytes);  // both CTAs' slabs
           ptx::tma_load_2d_pair(a_smem(s), &tmA, leader_full, kb * BK, tl.m0 + (int)rank * 128);
           ptx::tma_load_2d_pair(b_smem(s), &tmB, leader_full, kb * BK, tl.n0 + (int)rank * 128);
+          if (t == pair && kb == 0) FM_TRACE_MARK(p, 2);
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
       }
@@ -136,6 +139,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          if (kb == 0) FM_TRACE_MARK(p, 3);
           ptx::tc_fence_after();
           const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_smem(s));
           const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_smem(s));
@@ -147,6 +151,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
         if (!ok) break;
+        FM_TRACE_MARK(p, 4);
         ptx::umma_commit_pair(tfull_bar(acc), 0x3);  // accumulator halves complete in both CTAs
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
@@ -167,6 +172,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       bool ok = ptx::mbar_wait(tfull_bar(acc), acc_ph, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (threadIdx.x == 64) FM_TRACE_MARK(p, 5);
       ptx::tc_fence_after();
 #pragma unroll 1
       for (int ch = 0; ch < 8; ++ch) {
@@ -182,6 +188,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             reinterpret_cast<uint4*>(dcur)[v] = reinterpret_cast<const uint4*>(dnext)[v];
         }
       }
+      if (threadIdx.x == 64) FM_TRACE_MARK(p, 6);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0));
@@ -201,6 +208,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     ptx::tc_fence_after();
     ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) FM_TRACE_MARK(p, 7);
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 0x47320000u | (unsigned)blockIdx.x);
 }
 
