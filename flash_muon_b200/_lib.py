@@ -38,6 +38,8 @@ SIGNATURES = {
     "fm_ns_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "fm_newtonschulz": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p,
                                 c_void_p, c_size_t, c_int, c_void_p]),
+    "fm_newtonschulz_static": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p,
+                                       c_int, c_void_p]),
     "fm_normalize": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_int64,
                              c_void_p, c_int64, c_void_p, c_void_p]),
     "fm_norm_scratch_floats": (c_size_t, []),
@@ -59,7 +61,7 @@ class FlashMuonError(RuntimeError):
 def _load() -> ctypes.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m flash_muon_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python flash_muon_b200/build.py` "
             "(there is no CPU or Triton fallback)")
     lib = ctypes.CDLL(str(LIB_PATH))
     for name, (res, args) in SIGNATURES.items():

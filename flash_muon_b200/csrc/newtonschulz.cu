@@ -11,6 +11,8 @@
 // flash_muon/matmul_transpose_triton.py:88).
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "gemm_tc.cuh"
 
@@ -218,4 +220,65 @@ extern "C" int fm_newtonschulz(const void* G, int64_t rows, int64_t cols, int64_
     cur ^= 1;
   }
   return FM_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Newton-Schulz without a caller workspace, for hosts that may not allocate device memory.
+// The scratch of fm_newtonschulz (both orientations of the iterate twice, A, B, the partial
+// sums) lives in one file-scope device array; every device that loads the library carries it
+// until the process ends.  The name of the array is only a host-side handle: the device address
+// is looked up once per device with cudaGetSymbolAddress and that pointer is what the kernels get.
+namespace fm {
+namespace {
+
+constexpr int64_t kStaticMaxSmall = 1024;  // largest min(rows, cols)
+constexpr int64_t kStaticMaxLarge = 4096;  // largest max(rows, cols)
+constexpr size_t kStaticScratchBytes =
+    (size_t)(4 * kStaticMaxSmall * kStaticMaxLarge + 2 * kStaticMaxSmall * kStaticMaxSmall) * 2 +
+    8192;  // + partial sums and the 256-byte rounding of the seven regions
+
+static __device__ __align__(256) unsigned char g_ns_static_scratch[kStaticScratchBytes];
+
+// Device address of the scratch array on the current device, resolved on first use.
+int static_scratch_ptr(void** out) {
+  static std::mutex mu;
+  static void* ptrs[64] = {nullptr};
+  int dev = 0;
+  FM_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(FM_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_ns_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(FM_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s",
+                  cudaGetErrorString(e));
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return FM_OK;
+}
+
+}  // namespace
+}  // namespace fm
+
+extern "C" int fm_newtonschulz_static(const void* G, int64_t rows, int64_t cols, int64_t ldg,
+                                      int g_dtype, int steps, void* out, int flags, void* stream) {
+  using namespace fm;
+  clear_error();
+  if (rows <= 0 || cols <= 0) return fail(FM_ERR_INVALID, "bad extents");
+  const int64_t small = rows <= cols ? rows : cols, large = rows <= cols ? cols : rows;
+  NsLayout L;
+  if (small > kStaticMaxSmall || large > kStaticMaxLarge || !ns_layout(rows, cols, &L) ||
+      L.total > kStaticScratchBytes)
+    return fail(FM_ERR_WORKSPACE,
+                "fm_newtonschulz_static handles matrices up to %lld x %lld (either orientation); "
+                "got %lld x %lld -- use fm_newtonschulz with a caller workspace",
+                (long long)kStaticMaxSmall, (long long)kStaticMaxLarge, (long long)rows,
+                (long long)cols);
+  void* scratch = nullptr;
+  const int rc = static_scratch_ptr(&scratch);
+  if (rc != FM_OK) return rc;
+  return fm_newtonschulz(G, rows, cols, ldg, g_dtype, steps, out, scratch, kStaticScratchBytes,
+                         flags, stream);
 }

@@ -105,6 +105,26 @@ int fm_newtonschulz(const void* G, int64_t rows, int64_t cols, int64_t ldg, int 
                     void* out, void* workspace, size_t workspace_bytes, int flags, void* stream);
 
 /*
+ * fm_newtonschulz for callers that cannot allocate device memory -- a plugin running inside a
+ * host that owns the allocator, code already inside a stream capture, a real-time loop that must
+ * not touch cudaMalloc.  Same arguments and result as fm_newtonschulz, minus the workspace: the
+ * scratch is a fixed array inside the library (about 38 MB per GPU, resident from the moment the
+ * library's device code is loaded until the process exits).  This entry point has no counterpart
+ * in the reference, which allocates two buffers and several temporaries per call
+ * (flash_muon/muon.py:19-20, :23-29).
+ *  - Limit: min(rows, cols) <= 1024 and max(rows, cols) <= 4096; larger inputs are rejected with
+ *    FM_ERR_WORKSPACE and a message, nothing is launched.
+ *  - The first call on each device resolves the array's device address (one
+ *    cudaGetSymbolAddress with that device current); make that call before any stream capture.
+ *    No call allocates or frees memory.
+ *  - All calls on a device share the one array.  Nothing in it has to start at zero (every region
+ *    is written before it is read), but two calls whose kernels overlap on the GPU -- different
+ *    streams, or different host threads -- race on it: serialise them on one stream.
+ */
+int fm_newtonschulz_static(const void* G, int64_t rows, int64_t cols, int64_t ldg, int g_dtype,
+                           int steps, void* out, int flags, void* stream);
+
+/*
  * Frobenius normalisation used by fm_newtonschulz, exported for tests:
  * xd[rows,cols] (row pitch ldxd) = bf16(G) / (||bf16(G)||_F + 1e-7) and xt[cols,rows] (row pitch
  * ldxt) = its transpose, with the reference's roundings (norm, sum and quotient each rounded to
