@@ -71,7 +71,7 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                 "--format=csv,noheader,nounits", "-lms", "200"],
+                 "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -242,12 +242,13 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
-    # ---- device-resident leg: gradients already in HBM
-    for _ in range(args.warmup):
-        opt.step()
-    sync()
+    # ---- device-resident leg: gradients already in HBM.  Clock samples cover the warm-up steps
+    # as well (same load), so that short timed regions still get several samples.
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
+        for _ in range(args.warmup):
+            opt.step()
+        sync()
         e0.record()
         for _ in range(args.steps):
             opt.step()

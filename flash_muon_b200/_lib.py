@@ -44,6 +44,12 @@ SIGNATURES = {
                              c_void_p, c_int64, c_void_p, c_void_p]),
     "fm_norm_scratch_floats": (c_size_t, []),
     "fm_momentum": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_double, c_int, c_void_p]),
+    "fm_ipc_export": (c_int, [c_void_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_uint64)]),
+    "fm_ipc_import": (c_int, [ctypes.c_char_p, ctypes.c_uint64, ctypes.POINTER(c_void_p)]),
+    "fm_ipc_close_all": (c_int, []),
+    "fm_copy_async": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+    "fm_stream_write32": (c_int, [c_void_p, ctypes.c_uint32, c_void_p]),
+    "fm_stream_wait32_geq": (c_int, [c_void_p, ctypes.c_uint32, c_void_p]),
     "fm_update_multi": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                 ctypes.POINTER(c_int64), ctypes.POINTER(c_double), c_int, c_int,
                                 c_double, c_void_p]),

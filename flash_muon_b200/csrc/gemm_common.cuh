@@ -25,6 +25,7 @@ struct GemmParams {
   int d_vec;      // D rows can be read with 16-byte loads
   int c_vec;      // C rows can be written with 16-byte stores
   int t_pack;     // CT can be written as pairs of adjacent rows (4-byte stores)
+  int stages;     // depth of the shared-memory ring (CTA-pair kernel)
   unsigned int* err;
 #ifdef FM_TRACE
   unsigned long long* trace;  // diagnostic builds only: 8 timestamps per CTA

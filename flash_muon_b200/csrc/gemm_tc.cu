@@ -319,6 +319,7 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
             (a.ldc_c == 1) && (a.ldc_r % 8 == 0);
   p.t_pack = (a.CT != nullptr) && (a.ldt_c == 1) && (a.ldt_r % 2 == 0) &&
              ((reinterpret_cast<uintptr_t>(a.CT) & 3u) == 0);
+  p.stages = 0;
   p.err = device_error_word();
 #ifdef FM_TRACE
   p.trace = g_trace_ptr;

@@ -13,6 +13,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "gemm_tc.cuh"
@@ -25,11 +27,11 @@ constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr int kSlabBytes = 128 * BK * 2;      // 16 KiB: 128 rows x 64 columns of 16-bit values
-constexpr int kStages = 6;
+constexpr int kMaxStages = 6;
 constexpr int kStageBytes = 2 * kSlabBytes;   // this CTA's A slab + B slab
 constexpr int kTmemCols = 512;                // two accumulators of 256 fp32 columns
-constexpr int kNumBars = 2 * kStages + 4;
-constexpr int kSmemBytes = kStages * kStageBytes + kNumBars * 8 + 16 + 1024;
+constexpr int kNumBars = 2 * kMaxStages + 4;
+constexpr int smem_bytes(int stages) { return stages * kStageBytes + kNumBars * 8 + 16 + 1024; }
 
 struct Tile2 {
   int m0, n0;  // first row / column of the 256 x 256 tile
@@ -60,15 +62,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  const int kStages = p.stages;  // ring depth chosen by the host (shared memory left to others)
   const uint32_t smem_base = ptx::smem_u32(smem);
   const uint32_t bar_base = smem_base + kStages * kStageBytes;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kStages * kStageBytes + kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
   auto a_smem = [&](int s) { return smem_base + s * kStageBytes; };
   auto b_smem = [&](int s) { return smem_base + s * kStageBytes + kSlabBytes; };
 
@@ -212,10 +215,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 0x47320000u | (unsigned)blockIdx.x);
 }
 
+// Ring depth: 6 stages of 32 KiB; 4 cost 2-3 % on the large products, 3 cost 12 %.
+int pair_stages() {
+  static int cached = 0;
+  if (cached == 0) {
+    int v = kMaxStages;
+    if (const char* e = getenv("FM_GEMM_STAGES")) {
+      const int w = atoi(e);
+      if (w >= 2 && w <= kMaxStages) v = w;
+    }
+    cached = v;
+  }
+  return cached;
+}
+
 template <typename T>
 int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int max_pairs,
             cudaStream_t stream) {
   const int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
+  p.stages = pair_stages();
+  const int kSmemBytes = smem_bytes(p.stages);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   cfg.blockDim = dim3(kThreads);
@@ -239,8 +258,9 @@ int max_pairs_for() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
   if (cached[dev] == 0) {
+    const int kSmemBytes = smem_bytes(pair_stages());
     if (cudaFuncSetAttribute(gemm_tc2_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemBytes) != cudaSuccess)
+                             smem_bytes(kMaxStages)) != cudaSuccess)
       return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2);

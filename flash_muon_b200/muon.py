@@ -9,15 +9,21 @@ What differs is how the device work is issued:
   this rank's slot of the gather buffer (no ``.flatten()`` copy, no staging tensor);
 * the gather buffer is double-buffered, so round ``i+1`` may fill its slot while round ``i`` is
   still being gathered and applied;
-* the all-gather is in place (NCCL over NVLink via ``torch.distributed``), launched asynchronously
-  so that it overlaps the next round's Newton-Schulz exactly like the reference's
-  ``async_op=True`` call (flash_muon/muon.py:106-108);
+* the all-gather (flash_muon/muon.py:106-108) overlaps the next round's Newton-Schulz like the
+  reference's ``async_op=True`` call.  Inside one box it is done by DMA copy engines pushing
+  each finished slot into the peers' buffers, ordered by stream-side flags
+  (``peer_gather.py``): NCCL's all-gather kernel cannot become resident next to the persistent
+  GEMM kernels, a copy engine needs no SM.  ``FM_MUON_GATHER=nccl`` (or a failed peer set-up)
+  selects the in-place NCCL all-gather through ``torch.distributed`` instead;
 * weight decay + scaled update of all ``world_size`` parameters of a round is one multi-tensor
-  kernel (``fm_update_multi``) instead of ``2 * world_size`` launches.
+  kernel (``fm_update_multi``) instead of ``2 * world_size`` launches, enqueued on a second
+  stream so that this HBM-bound pass runs under the tensor-core work of the following rounds.
 """
 from __future__ import annotations
 
 import ctypes
+import os
+import warnings
 
 import torch
 import torch.distributed as dist
@@ -41,6 +47,8 @@ class Muon(torch.optim.Optimizer):
 
     # Device of the gather buffers ("cuda" = the current CUDA device, flash_muon/muon.py:69).
     _buffer_device = "cuda"
+    # Apply the decay + update of a finished round on a second stream, under the next GEMMs.
+    _overlap_updates = True
 
     def __init__(self, params, lr=0.02, weight_decay=0.01, momentum=0.95, nesterov=True,
                  ns_steps=5, rank=None, world_size=None):
@@ -64,6 +72,7 @@ class Muon(torch.optim.Optimizer):
             param_groups.append(group)
         super().__init__(param_groups, defaults)
         self._workspace: Tensor | None = None
+        self._peer = None          # PeerGather once set up; False if NCCL is to be used
 
     # ------------------------------------------------------------------ helpers
     def _ns_workspace(self, rows: int, cols: int, device) -> Tensor:
@@ -97,6 +106,27 @@ class Muon(torch.optim.Optimizer):
         # in place: `slot` is row `rank` of `buffer`                    (flash_muon/muon.py:108)
         return dist.all_gather_into_tensor(buffer, slot, async_op=True)
 
+    def _peer_gather(self):
+        """The copy-engine all-gather, set up collectively on first use (None: use NCCL)."""
+        if self._peer is None:
+            self._peer = False
+            want = os.environ.get("FM_MUON_GATHER", "peer") != "nccl"
+            if want and self.world_size > 1 and self.param_groups[0]["update_buffer"].is_cuda:
+                from .peer_gather import PeerGather
+                ok, peer = 1, None
+                try:
+                    peer = PeerGather(self.rank, self.world_size,
+                                      [(g["update_buffer"], g["update_buffer_alt"])
+                                       for g in self.param_groups])
+                except Exception as exc:  # same decision on every rank, taken below
+                    ok = 0
+                    warnings.warn(f"peer all-gather unavailable ({exc}); using NCCL")
+                flag = torch.tensor([ok], device=self.param_groups[0]["update_buffer"].device)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if int(flag.item()) == 1:
+                    self._peer = peer
+        return self._peer or None
+
     def _apply_updates(self, params_world, views, lr, weight_decay):
         # p *= 1 - lr*wd ; p += -lr*sqrt(max(1, rows/cols)) * g      (flash_muon/muon.py:87-89)
         stream_ptr = current_stream_ptr(views[0].device)
@@ -116,25 +146,61 @@ class Muon(torch.optim.Optimizer):
                                       stream_ptr))
 
     # ------------------------------------------------------------------ step
+    def _side_stream(self, device):
+        st = getattr(self, "_side", None)
+        if st is None or st.device != device:
+            self._side = st = torch.cuda.Stream(device=device)
+        return st
+
     @torch.no_grad()
     def step(self):
         ws = self.world_size
-        for group in self.param_groups:
+        overlap = self._overlap_updates and len(self.param_groups) > 0 and \
+            self.param_groups[0]["update_buffer"].is_cuda
+        if overlap:
+            device = self.param_groups[0]["update_buffer"].device
+            main = torch.cuda.current_stream(device)
+            side = self._side_stream(device)
+        peer = self._peer_gather() if (ws > 1 and type(self)._all_gather is Muon._all_gather) else None
+        for gi, group in enumerate(self.param_groups):
             buffers = (group["update_buffer"], group["update_buffer_alt"])
             views = (group["update_buffer_views"], group["update_buffer_alt_views"])
             params: list[Tensor] = group["params"]
             handle = None
             params_world = None
-            prev = 0  # which buffer the round in flight uses
+            prev = 0                   # which buffer the round in flight uses
+            ns_done = [None, None]     # per buffer: this rank's slot has been written (main stream)
+            upd_done = [None, None]    # per buffer: its updates have been applied (side stream)
 
             def update_prev():
-                if handle is not None:
-                    handle.wait()
-                self._apply_updates(params_world, views[prev], group["lr"], group["weight_decay"])
+                if not overlap:
+                    if handle is not None:
+                        handle.wait()
+                    self._apply_updates(params_world, views[prev], group["lr"], group["weight_decay"])
+                    if hasattr(handle, "done"):
+                        handle.done()
+                    return
+                # The update only streams parameters through HBM; on its own stream it runs under
+                # the tensor-core work of the following rounds instead of between them.
+                if ns_done[prev] is not None:
+                    side.wait_event(ns_done[prev])  # this rank's own slot is complete
+                with torch.cuda.stream(side):
+                    if handle is not None:
+                        handle.wait()
+                    self._apply_updates(params_world, views[prev], group["lr"], group["weight_decay"])
+                    if hasattr(handle, "done"):
+                        handle.done()  # peers may overwrite their slots of this buffer
+                    upd_done[prev] = torch.cuda.Event()
+                    upd_done[prev].record(side)
 
             for round_idx, base_i in enumerate(range(0, len(params), ws)):
                 cur = round_idx & 1
                 slot = views[cur][self.rank]
+                if overlap and upd_done[cur] is not None:
+                    main.wait_event(upd_done[cur])  # buffer `cur` is free to be overwritten
+                    upd_done[cur] = None
+                if peer is not None:
+                    peer.before_slot_write(gi, cur, torch.cuda.current_stream(slot.device))
                 if base_i + self.rank < len(params):
                     p = params[base_i + self.rank]
                     g = p.grad
@@ -147,12 +213,21 @@ class Muon(torch.optim.Optimizer):
                     if g.ndim == 4:  # for the case of conv filters
                         g = g.view(len(g), -1)
                     self._orthogonalize(g, slot, group["ns_steps"])
+                    if overlap:
+                        ns_done[cur] = torch.cuda.Event()
+                        ns_done[cur].record(main)
+                else:
+                    ns_done[cur] = None
                 # an idle rank contributes whatever its slot holds (muon.py:104-105)
                 if base_i > 0:
                     update_prev()
-                if ws > 1:
+                if peer is not None:
+                    handle = peer.publish(gi, cur, slot, list(range(min(ws, len(params) - base_i))))
+                elif ws > 1:
                     handle = self._all_gather(buffers[cur], slot)
                 params_world = params[base_i: base_i + ws]
                 prev = cur
             if params_world is not None:
                 update_prev()
+        if overlap:
+            main.wait_stream(side)  # the step's effects are ordered on the caller's stream

@@ -153,6 +153,30 @@ int fm_momentum(void* grad, void* buf, int64_t n, int dtype, double momentum, in
 int fm_update_multi(void* const* params, const void* const* updates, const int64_t* numels,
                     const double* alphas, int count, int p_dtype, double decay, void* stream);
 
+/*
+ * Peer-memory plumbing of the copy-engine all-gather that stands in for
+ * dist.all_gather_into_tensor (flash_muon/muon.py:108) inside one NVLink-connected box.  Each rank
+ * copies its finished slot into every peer's gather buffer with DMA engines and orders the
+ * exchange with 32-bit flags written and awaited by the streams themselves, so no SM is taken from
+ * the Newton-Schulz GEMMs the transfer overlaps.
+ *  fm_ipc_export : CUDA IPC handle (64 bytes) of the allocation that contains `ptr`, and the byte
+ *                  offset of `ptr` inside it.
+ *  fm_ipc_import : address, in this process, of offset `offset` of a peer's exported allocation
+ *                  (opened once per handle and device, peer access enabled on first use).
+ *  fm_ipc_close_all : closes every imported allocation.
+ *  fm_copy_async : device-to-device cudaMemcpyAsync on `stream`; dst / src may be peer addresses.
+ *  fm_stream_write32 : `stream` stores `value` to the 4-byte aligned device word `addr` (local or
+ *                  peer) after all prior work of the stream.
+ *  fm_stream_wait32_geq : `stream` stalls until (int32)(*addr - value) >= 0; later work of the
+ *                  stream sees remote writes that preceded the flag.  No host thread blocks.
+ */
+int fm_ipc_export(const void* ptr, unsigned char* handle64, uint64_t* offset);
+int fm_ipc_import(const unsigned char* handle64, uint64_t offset, void** ptr);
+int fm_ipc_close_all(void);
+int fm_copy_async(void* dst, const void* src, size_t bytes, void* stream);
+int fm_stream_write32(void* addr, uint32_t value, void* stream);
+int fm_stream_wait32_geq(const void* addr, uint32_t value, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

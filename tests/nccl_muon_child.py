@@ -1,4 +1,5 @@
-"""One NCCL rank of ``test_two_ranks_nccl_match_single_rank`` (launched by torchrun)."""
+"""One rank of the multi-GPU ``Muon.step`` tests (launched by torchrun): runs two steps and saves
+the parameters; ``FM_MUON_GATHER`` selects the copy-engine or the NCCL all-gather."""
 import os
 import sys
 from pathlib import Path
@@ -30,8 +31,11 @@ def main():
         opt.step()
     torch.cuda.synchronize()
     fm._lib.device_status()
+    dist.barrier()
     owned = sorted(i for i, p in enumerate(ps) if "momentum_buffer" in opt.state[p])
-    torch.save({"params": [p.detach().cpu() for p in ps], "owned": owned}, sys.argv[1] + f".rank{rank}")
+    mode = "peer" if opt._peer else "nccl"
+    torch.save({"params": [p.detach().cpu() for p in ps], "owned": owned, "mode": mode},
+               sys.argv[1] + f".rank{rank}")
     dist.barrier()
     dist.destroy_process_group()
 

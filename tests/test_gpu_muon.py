@@ -126,20 +126,31 @@ def test_missing_grad_asserts():
         opt.step()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_ranks_nccl_match_single_rank(tmp_path):
-    """world_size 2 over NCCL: both ranks end with identical parameters, equal to world_size 1."""
+def _run_ranks(tmp_path, ws, gather):
     child = ROOT / "tests" / "nccl_muon_child.py"
-    out = tmp_path / "res"
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-           "--master-addr", "127.0.0.1", "--master-port", "29733", str(child), str(out)]
-    env = {**os.environ, "NCCL_NVLS_ENABLE": "0"}
+    out = tmp_path / f"res_{gather}_{ws}"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ws}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29733 + ws + (7 if gather == "nccl" else 0)),
+           str(child), str(out)]
+    env = {**os.environ, "NCCL_NVLS_ENABLE": "0", "FM_MUON_GATHER": gather}
     assert subprocess.run(cmd, env=env, timeout=600).returncode == 0
-    r0, r1 = torch.load(str(out) + ".rank0"), torch.load(str(out) + ".rank1")
+    return [torch.load(str(out) + f".rank{r}") for r in range(ws)]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("gather", ["peer", "nccl"])
+def test_ranks_match_single_rank(tmp_path, gather):
+    """All ranks end with identical parameters, bit-equal to world_size 1, with the copy-engine
+    all-gather (DMA pushes ordered by stream-side flags) as with the NCCL one.  Uses every GPU of
+    the box up to 4 (3 gives a partial last round)."""
+    ws = min(torch.cuda.device_count(), 4)
+    ws = 3 if ws == 4 else ws
+    res = _run_ranks(tmp_path, ws, gather)
+    assert all(r["mode"] == gather for r in res)
     params, grads = muon_case(2, shapes=MUON_SHAPES + gpt2_medium_shapes(1), seed=9)
     ps, _ = run_product(params, grads, 2, **MUON_HP)
-    for a, b, c in zip(r0["params"], r1["params"], ps):
-        assert torch.equal(a, b)
-        assert torch.equal(a, c.detach().cpu())
-    assert sorted(r0["owned"] + r1["owned"]) == list(range(len(params)))
-    assert not set(r0["owned"]) & set(r1["owned"])
+    for i, c in enumerate(ps):
+        for r in res:
+            assert torch.equal(r["params"][i], c.detach().cpu())
+    owned = sorted(i for r in res for i in r["owned"])
+    assert owned == list(range(len(params)))
