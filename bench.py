@@ -197,10 +197,12 @@ def time_syrk(peaks, dim=SYRK_DIM, reps=30):
     res = {"shape": [m, k], "ms": t, "tflops_effective": 2 * m * m * k / t / 1e9,
            "tflops_algorithmic": alg / t / 1e9, "tflops_executed": execd / t / 1e9,
            "cublas_ms": tc, "speedup_vs_cublas": tc / t, "reps": reps}
-    roof = {"kernel": f"gemm_tc_kernel<bf16,256> as matmul_transpose {m}x{k}", "bound": "tensor",
+    # DRAM bytes of one 8192^2 launch from an ncu capture (profiles/gemm_tc2_kernel_syrk_8192_bf16.md)
+    traffic = 682.5e6 + 116.6e6 if m == 8192 else None
+    roof = {"kernel": f"gemm_tc2_kernel<bf16> as matmul_transpose {m}x{k}", "bound": "tensor",
             "achieved": alg / t / 1e9, "peak": peaks["bf16"], "unit": "TFLOP/s",
             "frac": alg / t / 1e9 / peaks["bf16"], "frac_executed": execd / t / 1e9 / peaks["bf16"],
-            "traffic": None, "peak_source": f"{peaks['source']} burst (kernel timed alone)"}
+            "traffic": traffic, "peak_source": f"{peaks['source']} burst (kernel timed alone)"}
     return res, roof
 
 
@@ -277,13 +279,33 @@ def run_ours(args):
     host_p = {s: torch.empty(*s, dtype=torch.bfloat16).pin_memory() for s in set(LLAMA_LAYER)}
     h2d = sum(p.numel() * 2 for p in owned)
     d2h = h2d
+    owned_set = set(owned)
+    up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
 
     def e2e_step():
-        for p in owned:
-            p.grad.copy_(host_g[tuple(p.shape)], non_blocking=True)
-        opt.step()
-        for p in owned:
-            host_p[tuple(p.shape)].copy_(p.detach(), non_blocking=True)
+        # Gradients stream in on a copy stream in the order the step consumes them; the step
+        # waits per parameter.  Updated parameters stream out as soon as their round is applied.
+        main = torch.cuda.current_stream(dev)
+        up.wait_stream(main)      # the previous step is done with the gradient buffers
+        ready = {}
+        with torch.cuda.stream(up):
+            for p in owned:
+                p.grad.copy_(host_g[tuple(p.shape)], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(up)
+                ready[p] = ev
+
+        def applied(ps, stream):
+            ev = torch.cuda.Event()
+            ev.record(stream)
+            down.wait_event(ev)
+            with torch.cuda.stream(down):
+                for p in ps:
+                    if p in owned_set:
+                        host_p[tuple(p.shape)].copy_(p.detach(), non_blocking=True)
+
+        opt.step(grad_ready=ready, on_applied=applied)
+        main.wait_stream(down)    # the step's result is on the host when the stream gets here
 
     e2e_step()
     sync()
@@ -313,7 +335,7 @@ def run_ours(args):
         "step_tflops_algorithmic": alg / ms / 1e9, "step_tflops_cublas_equivalent": full / ms / 1e9,
         "step_frac_of_sustained_peak": alg / ms / 1e9 / ws / peaks["bf16_sustained"],
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps": k2, "note": "per rank: owned gradients from pinned host memory, owned parameters back"},
+                "steps": k2, "note": "per rank: owned gradients from pinned host memory, owned parameters back to pinned host memory; copies are streamed per parameter through Muon.step(grad_ready=, on_applied=) and all lie inside the timed region"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }

@@ -153,7 +153,19 @@ class Muon(torch.optim.Optimizer):
         return st
 
     @torch.no_grad()
-    def step(self):
+    def step(self, *, grad_ready=None, on_applied=None):
+        """One optimizer step (flash_muon/muon.py:75-110; no closure, returns None).
+
+        Two optional hooks let a caller stream tensors through the step instead of waiting for
+        whole-model copies on either side of it:
+
+        * ``grad_ready``: mapping parameter -> ``torch.cuda.Event``; the step waits for the event
+          on its stream before it first touches that parameter's gradient (e.g. the event of a
+          host-to-device copy still in flight).
+        * ``on_applied(params, stream)``: called right after the decay + update of a round's
+          parameters has been enqueued on ``stream``; work the callback enqueues behind an event
+          of that stream (e.g. device-to-host copies) sees the updated parameters.
+        """
         ws = self.world_size
         overlap = self._overlap_updates and len(self.param_groups) > 0 and \
             self.param_groups[0]["update_buffer"].is_cuda
@@ -179,6 +191,8 @@ class Muon(torch.optim.Optimizer):
                     self._apply_updates(params_world, views[prev], group["lr"], group["weight_decay"])
                     if hasattr(handle, "done"):
                         handle.done()
+                    if on_applied is not None:
+                        on_applied(params_world, torch.cuda.current_stream(views[prev][0].device))
                     return
                 # The update only streams parameters through HBM; on its own stream it runs under
                 # the tensor-core work of the following rounds instead of between them.
@@ -190,6 +204,8 @@ class Muon(torch.optim.Optimizer):
                     self._apply_updates(params_world, views[prev], group["lr"], group["weight_decay"])
                     if hasattr(handle, "done"):
                         handle.done()  # peers may overwrite their slots of this buffer
+                    if on_applied is not None:
+                        on_applied(params_world, side)
                     upd_done[prev] = torch.cuda.Event()
                     upd_done[prev].record(side)
 
@@ -205,6 +221,8 @@ class Muon(torch.optim.Optimizer):
                     p = params[base_i + self.rank]
                     g = p.grad
                     assert g is not None
+                    if grad_ready is not None and p in grad_ready:
+                        torch.cuda.current_stream(g.device).wait_event(grad_ready[p])
                     state = self.state[p]
                     if "momentum_buffer" not in state:
                         state["momentum_buffer"] = torch.zeros_like(g)

@@ -119,6 +119,41 @@ def test_state_dict_layout_and_side_effects():
         assert torch.equal(p, b)
 
 
+def test_streaming_hooks_give_the_same_step():
+    """Gradients arriving through a copy stream (grad_ready) and parameters leaving through
+    on_applied: same parameters as the plain step, every parameter reported exactly once."""
+    params, grads = muon_case(1)
+    ref, _ = run_product(params, grads, 1, **MUON_HP)
+    ps = [torch.nn.Parameter(p.to(DEV)) for p in params]
+    opt = fm.Muon(ps, rank=0, world_size=1, **MUON_HP)
+    host = [g.pin_memory() for g in grads[0]]
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+    ready, seen, out = {}, [], {}
+    for p in ps:
+        p.grad = torch.zeros_like(p)
+    with torch.cuda.stream(up):
+        for p, h in zip(ps, host):
+            p.grad.copy_(h, non_blocking=True)
+            ready[p] = torch.cuda.Event()
+            ready[p].record(up)
+
+    def applied(plist, stream):
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        down.wait_event(ev)
+        with torch.cuda.stream(down):
+            for p in plist:
+                seen.append(p)
+                out[p] = torch.empty(p.shape, dtype=p.dtype).pin_memory()
+                out[p].copy_(p.detach(), non_blocking=True)
+
+    opt.step(grad_ready=ready, on_applied=applied)
+    torch.cuda.synchronize()
+    assert len(seen) == len(ps) and set(seen) == set(ps)
+    for p, r in zip(ps, ref):
+        assert torch.equal(p, r) and torch.equal(out[p], r.detach().cpu())
+
+
 def test_missing_grad_asserts():
     p = torch.nn.Parameter(torch.randn(32, 32, device=DEV).bfloat16())
     opt = fm.Muon([p], rank=0, world_size=1)

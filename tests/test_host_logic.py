@@ -49,7 +49,11 @@ def test_muon_signature_matches_reference():
     d = {k: v.default for k, v in sig.parameters.items()}
     assert (d["lr"], d["weight_decay"], d["momentum"], d["nesterov"], d["ns_steps"]) == \
         (0.02, 0.01, 0.95, True, 5)
-    assert list(inspect.signature(fm.Muon.step).parameters) == ["self"]
+    # step() takes no positional argument, like the reference; the two extras are keyword-only
+    step = inspect.signature(fm.Muon.step).parameters
+    assert list(step) == ["self", "grad_ready", "on_applied"]
+    assert all(step[k].kind is inspect.Parameter.KEYWORD_ONLY and step[k].default is None
+               for k in ("grad_ready", "on_applied"))
 
 
 def _free_port() -> int:
