@@ -26,6 +26,12 @@ struct GemmParams {
   int c_vec;      // C rows can be written with 16-byte stores
   int t_pack;     // CT can be written as pairs of adjacent rows (4-byte stores)
   int stages;     // depth of the shared-memory ring (CTA-pair kernel)
+  // balanced tail of the CTA-pair kernel (all zero: every tile is dealt whole)
+  int sk_dp_tiles;         // tiles dealt whole, round-robin; the rest is cut by K blocks
+  int sk_per;              // K blocks per pair in the balanced region
+  long long sk_total;      // K blocks of the balanced region
+  float* sk_ws;            // scratch for partial accumulators
+  unsigned int* sk_cnt;    // per (tile, CTA rank) count of deposited parts, zero between launches
   unsigned int* err;
 #ifdef FM_TRACE
   unsigned long long* trace;  // diagnostic builds only: 8 timestamps per CTA

@@ -14,6 +14,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 #include "gemm_common.cuh"
@@ -35,6 +36,59 @@ constexpr int smem_bytes(int stages) { return stages * kStageBytes + kNumBars * 
 
 struct Tile2 {
   int m0, n0;  // first row / column of the 256 x 256 tile
+};
+
+// Work of one CTA pair.  The first `sk_dp_tiles` tiles of the list are dealt round-robin, one
+// whole tile at a time.  The rest (between one and two waves' worth; empty unless the host
+// decides that balancing pays, see plan_schedule) is cut by K blocks into equal contiguous shares, so
+// that every pair finishes at the same time instead of most of them idling through a last
+// partial wave.  A pair walks its share from the END: first the range that begins a tile it
+// cannot finish -- that partial accumulator is deposited in fp32 scratch right away -- then
+// whole tiles, last the range that finishes a tile begun by earlier pairs.  There the deposits
+// of those pairs (made at the start of their shares, so long since complete) are added in a
+// fixed order to the accumulator and the tile's epilogue runs as usual.  The result does not
+// depend on timing; the wait for the deposits is a formality with the usual cycle limit.
+struct WorkItem {
+  int tile;      // index into the tile list
+  int kb0, kb1;  // K-block range
+  int sk_tile;   // index of the tile inside the balanced region
+  int deposit;   // 1: range stops short of the tile's last K block -> deposit, no epilogue
+  int gather;    // 1: range finishes a tile whose first K blocks were done by earlier pairs
+};
+
+struct WorkIter {
+  int dp_next, dp_step, dp_end;
+  long long lo, hi;
+  __device__ WorkIter(const GemmParams& p, int pair, int npairs) {
+    dp_next = pair;
+    dp_step = npairs;
+    dp_end = p.sk_dp_tiles;
+    lo = (long long)pair * p.sk_per;
+    hi = lo + p.sk_per;
+    if (hi > p.sk_total) hi = p.sk_total;
+    if (lo > hi) lo = hi;
+  }
+  __device__ bool next(const GemmParams& p, WorkItem& w) {
+    if (dp_next < dp_end) {
+      w.tile = dp_next; w.kb0 = 0; w.kb1 = p.num_kb; w.sk_tile = 0; w.deposit = 0; w.gather = 0;
+      dp_next += dp_step;
+      return true;
+    }
+    if (hi > lo) {
+      const int rel = (int)((hi - 1) / p.num_kb);
+      const long long t_begin = (long long)rel * p.num_kb;
+      const long long seg_lo = lo > t_begin ? lo : t_begin;
+      w.tile = p.sk_dp_tiles + rel;
+      w.sk_tile = rel;
+      w.kb0 = (int)(seg_lo - t_begin);
+      w.kb1 = (int)(hi - t_begin);
+      w.deposit = (w.kb1 != p.num_kb) ? 1 : 0;
+      w.gather = (w.kb0 != 0 && !w.deposit) ? 1 : 0;
+      hi = seg_lo;
+      return true;
+    }
+    return false;
+  }
 };
 
 __device__ __forceinline__ Tile2 decode_tile2(const GemmParams& p, int t) {
@@ -113,15 +167,18 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = pair; ok && t < p.num_tiles; t += npairs) {
-        const Tile2 tl = decode_tile2(p, t);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+      WorkIter it(p, pair, npairs);
+      WorkItem w;
+      bool first = true;
+      while (ok && it.next(p, w)) {
+        const Tile2 tl = decode_tile2(p, w.tile);
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t leader_full = ptx::mapa(full_bar(s), 0);
           if (rank == 0) ptx::mbar_expect_tx(full_bar(s), 4u * kSlabBytes);  // both CTAs' slabs
           ptx::tma_load_2d_pair(a_smem(s), &tmA, leader_full, kb * BK, tl.m0 + (int)rank * 128);
           ptx::tma_load_2d_pair(b_smem(s), &tmB, leader_full, kb * BK, tl.n0 + (int)rank * 128);
-          if (t == pair && kb == 0) FM_TRACE_MARK(p, 2);
+          if (first) { FM_TRACE_MARK(p, 2); first = false; }
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
       }
@@ -136,20 +193,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t acc_ph = 0;
       bool ok = true;
       const uint32_t idesc = ptx::make_idesc_f16(Num<T>::kFormat, 256, 256);
-      for (int t = pair; ok && t < p.num_tiles; t += npairs) {
+      WorkIter it(p, pair, npairs);
+      WorkItem w;
+      while (ok && it.next(p, w)) {
         if (!ptx::mbar_wait_cluster(tempty_bar(acc), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
-          if (kb == 0) FM_TRACE_MARK(p, 3);
+          if (kb == w.kb0) FM_TRACE_MARK(p, 3);
           ptx::tc_fence_after();
           const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_smem(s));
           const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_smem(s));
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             ptx::umma_f16_pair(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
-                               (uint32_t)((kb | k) != 0));
+                               (uint32_t)((kb != w.kb0) || (k != 0)));
           ptx::umma_commit_pair(empty_bar(s), 0x3);  // frees the stage in both CTAs
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
@@ -166,29 +225,108 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_ph = 0;
-    for (int t = pair; t < p.num_tiles; t += npairs) {
-      const Tile2 tl = decode_tile2(p, t);
-      const int row = tl.m0 + (int)rank * 128 + q * 32 + lane;
+    volatile int* sk_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    WorkIter it(p, pair, npairs);
+    WorkItem w;
+    while (it.next(p, w)) {
+      const Tile2 tl = decode_tile2(p, w.tile);
+      const int row_local = q * 32 + lane;
+      const int row = tl.m0 + (int)rank * 128 + row_local;
       const int bi = (tl.m0 >> 7) + (int)rank;
       alignas(16) T dcur[32], dnext[32];
-      epilogue_load_d<T>(p, row, tl.n0, dcur);
+      if (!w.deposit) epilogue_load_d<T>(p, row, tl.n0, dcur);
+
+      // parts of this tile deposited by earlier pairs: pairs c_first .. pair-1
+      int c_first = pair;
+      unsigned int* cnt = nullptr;
+      if (w.gather) {
+        c_first = (int)(((long long)w.sk_tile * p.num_kb) / p.sk_per);
+        cnt = p.sk_cnt + (w.sk_tile * 2 + (int)rank);
+        if (threadIdx.x == 64) {
+          const unsigned int need = (unsigned int)(pair - c_first);
+          const long long t0 = clock64();
+          int got = 0;
+          while (!got) {
+            const unsigned int v = *reinterpret_cast<volatile unsigned int*>(cnt);
+            got = (v >= need);
+            if (!got && (*abort_flag || clock64() - t0 > ptx::kWaitLimitCycles)) {
+              *abort_flag = 1;
+              break;
+            }
+          }
+          *sk_flag = got;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int got = *sk_flag;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (!got) break;
+        __threadfence();
+      }
+      // Deposit layout per (pair, CTA rank): [chunk 0..7][quad 0..7][row 0..127] float4, so that
+      // the 32 lanes of a warp (32 consecutive rows) touch 512 contiguous bytes per access.
+      auto part_ptr = [&](int c, int ch) {
+        return reinterpret_cast<const float4*>(p.sk_ws + ((size_t)(c * 2 + (int)rank) << 15)) +
+               (size_t)(ch * 8) * 128 + row_local;
+      };
+      float psum[32], pnext[32];
+      auto load_parts = [&](int ch, float (&dst)[32]) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[j] = 0.f;
+        for (int c = c_first; c < pair; ++c) {  // fixed order: by contributing pair
+          const float4* src = part_ptr(c, ch);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const float4 f = __ldcg(src + v * 128);
+            dst[4 * v] += f.x; dst[4 * v + 1] += f.y; dst[4 * v + 2] += f.z; dst[4 * v + 3] += f.w;
+          }
+        }
+      };
+      if (w.gather) load_parts(0, psum);
+
       bool ok = ptx::mbar_wait(tfull_bar(acc), acc_ph, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (threadIdx.x == 64) FM_TRACE_MARK(p, 5);
       ptx::tc_fence_after();
+      const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 256);
+      if (!w.deposit) {
 #pragma unroll 1
-      for (int ch = 0; ch < 8; ++ch) {
-        uint32_t raw[32];
-        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 256 + ch * 32),
-                           raw);
-        if (ch + 1 < 8) epilogue_load_d<T>(p, row, tl.n0 + (ch + 1) * 32, dnext);
-        ptx::tmem_ld_wait();
-        epilogue_store<T>(p, raw, dcur, row, tl.n0 + ch * 32, bi);
-        if (p.D != nullptr) {
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t raw[32];
+          ptx::tmem_ld_32x32(t_acc + (uint32_t)(ch * 32), raw);
+          if (ch + 1 < 8) {
+            epilogue_load_d<T>(p, row, tl.n0 + (ch + 1) * 32, dnext);
+            if (w.gather) load_parts(ch + 1, pnext);
+          }
+          ptx::tmem_ld_wait();
+          if (w.gather) {
 #pragma unroll
-          for (int v = 0; v < 4; ++v)
-            reinterpret_cast<uint4*>(dcur)[v] = reinterpret_cast<const uint4*>(dnext)[v];
+            for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(psum[j] + __uint_as_float(raw[j]));
+          }
+          epilogue_store<T>(p, raw, dcur, row, tl.n0 + ch * 32, bi);
+          if (p.D != nullptr) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              reinterpret_cast<uint4*>(dcur)[v] = reinterpret_cast<const uint4*>(dnext)[v];
+          }
+          if (w.gather) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) psum[j] = pnext[j];
+          }
+        }
+      } else {
+        // deposit this part of the tile (this CTA's 128 rows x 256 fp32 columns)
+        uint4* mine = reinterpret_cast<uint4*>(p.sk_ws + ((size_t)(pair * 2 + (int)rank) << 15)) +
+                      row_local;
+#pragma unroll 1
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t raw[32];
+          ptx::tmem_ld_32x32(t_acc + (uint32_t)(ch * 32), raw);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            mine[(size_t)(ch * 8 + v) * 128] =
+                make_uint4(raw[4 * v], raw[4 * v + 1], raw[4 * v + 2], raw[4 * v + 3]);
         }
       }
       if (threadIdx.x == 64) FM_TRACE_MARK(p, 6);
@@ -197,6 +335,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0));
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
+
+      if (w.deposit) {
+        // publish the deposit: all 128 threads' stores first, then one count
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) atomicAdd(p.sk_cnt + (w.sk_tile * 2 + (int)rank), 1u);
+      } else if (w.gather) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) *cnt = 0u;  // every deposit was consumed: ready for the next launch
+      }
     }
   }
 
@@ -229,10 +377,98 @@ int pair_stages() {
   return cached;
 }
 
+// Scratch of the balanced tail: per pair one partial accumulator (256 x 256 fp32: a pair leaves
+// at most one tile unfinished) and the deposit counters.  One set per device, resident while the library is loaded; it is lent to one
+// stream at a time (kernels of one stream run in order, so they can share it) and handed to
+// another stream only once the last kernel that used it has finished.  A launch that cannot have
+// it simply deals whole tiles.
+constexpr int kSkMaxPairs = 80;
+constexpr size_t kSkFloats = (size_t)kSkMaxPairs * 2 * 128 * 256;
+static __device__ __align__(256) float g_sk_ws[kSkFloats];
+static __device__ unsigned int g_sk_cnt[kSkMaxPairs * 4];
+
+struct SkScratch {
+  float* ws = nullptr;
+  unsigned int* cnt = nullptr;
+  cudaStream_t owner = nullptr;
+  bool owned = false;
+  cudaEvent_t last_use = nullptr;
+};
+
+// Returns the scratch if `stream` may use it for the launch being prepared, else nullptr.
+SkScratch* sk_acquire(cudaStream_t stream) {
+  static std::mutex mu;
+  static SkScratch per_dev[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  SkScratch& s = per_dev[dev];
+  if (s.ws == nullptr) {
+    void *a = nullptr, *b = nullptr;
+    if (cudaGetSymbolAddress(&a, g_sk_ws) != cudaSuccess ||
+        cudaGetSymbolAddress(&b, g_sk_cnt) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.last_use, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    s.ws = static_cast<float*>(a);
+    s.cnt = static_cast<unsigned int*>(b);
+  }
+  if (s.owned && s.owner != stream) {
+    if (cudaEventQuery(s.last_use) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;  // still in use by another stream
+    }
+  }
+  s.owner = stream;
+  s.owned = true;
+  return &s;
+}
+
+bool sk_enabled() {
+  const char* e = getenv("FM_GEMM_BALANCE");  // read per call: lets one process compare both
+  return !(e && atoi(e) == 0);
+}
+
+// Fills the schedule fields of `p` and returns the number of CTA pairs to launch.
+int plan_schedule(GemmParams& p, int max_pairs, cudaStream_t stream, SkScratch** used) {
+  const int T = p.num_tiles;
+  int P = T < max_pairs ? T : max_pairs;
+  p.sk_dp_tiles = T;
+  p.sk_per = 0;
+  p.sk_total = 0;
+  p.sk_ws = nullptr;
+  p.sk_cnt = nullptr;
+  *used = nullptr;
+  if (!sk_enabled() || max_pairs > kSkMaxPairs) return P;
+  // Worth it only when the idle time of the last partial wave exceeds what the partial sums
+  // cost.  Measured on B200 (same process, alternating): 8192^2 and 6144^2 products gain 7-10 %;
+  // lists of one or two waves, or tiles with K <= 4096, lose 2-15 %.  Model: a K block of a
+  // 256 x 256 tile takes ~0.41 us, depositing and re-reading partial accumulators ~12 us per
+  // pair, so balance when the K blocks saved, num_kb * (P - R) / P, are worth more than ~24 us.
+  if (T <= max_pairs) return P;
+  const int R = T % max_pairs;
+  if (R == 0) return P;
+  if ((long long)p.num_kb * (max_pairs - R) < 58LL * max_pairs) return P;
+  const int pairs = max_pairs;
+  const int dp_tiles = (T / max_pairs - 1) * max_pairs;  // leave between one and two waves to balance
+  SkScratch* sc = sk_acquire(stream);
+  if (sc == nullptr) return P;
+  const long long total = (long long)(T - dp_tiles) * p.num_kb;
+  p.sk_dp_tiles = dp_tiles;
+  p.sk_total = total;
+  p.sk_per = (int)((total + pairs - 1) / pairs);
+  p.sk_ws = sc->ws;
+  p.sk_cnt = sc->cnt;
+  *used = sc;
+  return pairs;
+}
+
 template <typename T>
 int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int max_pairs,
             cudaStream_t stream) {
-  const int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
+  SkScratch* used = nullptr;
+  const int pairs = plan_schedule(p, max_pairs, stream, &used);
   p.stages = pair_stages();
   const int kSmemBytes = smem_bytes(p.stages);
   cudaLaunchConfig_t cfg = {};
@@ -248,6 +484,7 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int m
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T>, tmA, tmB, p));
+  if (used != nullptr) FM_CUDA_CHECK(cudaEventRecord(used->last_use, stream));
   return FM_OK;
 }
 

@@ -111,6 +111,25 @@ def test_run_to_run_determinism():
     assert torch.equal(fm.matmul_transpose(x), fm.matmul_transpose(x))
 
 
+def test_balanced_tail_schedule(monkeypatch):
+    """A tile list of several waves with a short last wave and a long K is finished by cutting
+    the last tiles by K blocks (partial accumulators through fp32 scratch): same tolerance, exact
+    symmetry, run-to-run determinism, and within rounding of the whole-tile schedule."""
+    m, k = 3328, 5120   # 91 tiles of 256 x 256 on 74 CTA pairs, 80 K blocks
+    x = (torch.randn(m, k, device=DEV, generator=torch.Generator(device=DEV).manual_seed(5)) / k ** 0.5).bfloat16()
+    monkeypatch.setenv("FM_GEMM_BALANCE", "1")
+    y = torch.full((m, m), float("nan"), device=DEV, dtype=torch.bfloat16)
+    fm.matmul_transpose_assign(x, y)
+    check_syrk(x, y)
+    assert torch.equal(y, fm.matmul_transpose(x))
+    assert torch.equal(y, fm.matmul_transpose(x))
+    monkeypatch.setenv("FM_GEMM_BALANCE", "0")
+    whole = fm.matmul_transpose(x)
+    assert rel_fro(y, whole) <= 2e-3
+    assert rel_fro(whole, torch.matmul(x, x.T)) <= 2e-3
+    _lib.device_status()
+
+
 def test_empty_and_degenerate():
     assert fm.matmul_transpose(torch.empty(0, 16, device=DEV, dtype=torch.bfloat16)).shape == (0, 0)
     y = fm.matmul_transpose(torch.empty(5, 0, device=DEV, dtype=torch.bfloat16))
