@@ -21,6 +21,7 @@ What differs is how the device work is issued:
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 import warnings
@@ -49,6 +50,10 @@ class Muon(torch.optim.Optimizer):
     _buffer_device = "cuda"
     # Apply the decay + update of a finished round on a second stream, under the next GEMMs.
     _overlap_updates = True
+    # Alternate rounds between two streams: the GEMM kernels are persistent and statically
+    # scheduled, so a kernel's last wave leaves SMs idle; with an independent matrix in flight on
+    # the other stream its CTAs take those SMs.  Needs _overlap_updates (event-ordered rounds).
+    _two_lanes = True
 
     def __init__(self, params, lr=0.02, weight_decay=0.01, momentum=0.95, nesterov=True,
                  ns_steps=5, rank=None, world_size=None):
@@ -71,13 +76,15 @@ class Muon(torch.optim.Optimizer):
                          update_buffer_alt_views=[b2[i] for i in range(world_size)])
             param_groups.append(group)
         super().__init__(param_groups, defaults)
-        self._workspace: Tensor | None = None
+        self._workspaces: dict = {}   # lane -> Newton-Schulz scratch
+        self._lane = 0
         self._peer = None          # PeerGather once set up; False if NCCL is to be used
 
     # ------------------------------------------------------------------ helpers
     def _ns_workspace(self, rows: int, cols: int, device) -> Tensor:
+        """Newton-Schulz scratch of the lane (stream) the current round runs on."""
         need = newtonschulz_workspace_bytes(rows, cols)
-        ws = self._workspace
+        ws = self._workspaces.get(self._lane)
         if ws is None or ws.numel() < need or ws.device != device:
             # sized once for the largest matrix this rank owns
             biggest = need
@@ -86,7 +93,7 @@ class Muon(torch.optim.Optimizer):
                     if i % self.world_size == self.rank and p.ndim >= 2:
                         r = p.size(0)
                         biggest = max(biggest, newtonschulz_workspace_bytes(r, p.numel() // r))
-            self._workspace = ws = torch.empty(biggest, dtype=torch.uint8, device=device)
+            self._workspaces[self._lane] = ws = torch.empty(biggest, dtype=torch.uint8, device=device)
         return ws
 
     def _momentum(self, g: Tensor, buf: Tensor, momentum: float, nesterov: bool) -> Tensor:
@@ -169,10 +176,16 @@ class Muon(torch.optim.Optimizer):
         ws = self.world_size
         overlap = self._overlap_updates and len(self.param_groups) > 0 and \
             self.param_groups[0]["update_buffer"].is_cuda
+        lanes = None
         if overlap:
             device = self.param_groups[0]["update_buffer"].device
             main = torch.cuda.current_stream(device)
             side = self._side_stream(device)
+            if self._two_lanes:
+                if getattr(self, "_lane1", None) is None or self._lane1.device != device:
+                    self._lane1 = torch.cuda.Stream(device=device)
+                lanes = (main, self._lane1)
+                self._lane1.wait_stream(main)   # gradients produced on the caller's stream
         peer = self._peer_gather() if (ws > 1 and type(self)._all_gather is Muon._all_gather) else None
         for gi, group in enumerate(self.param_groups):
             buffers = (group["update_buffer"], group["update_buffer_alt"])
@@ -212,40 +225,46 @@ class Muon(torch.optim.Optimizer):
             for round_idx, base_i in enumerate(range(0, len(params), ws)):
                 cur = round_idx & 1
                 slot = views[cur][self.rank]
-                if overlap and upd_done[cur] is not None:
-                    main.wait_event(upd_done[cur])  # buffer `cur` is free to be overwritten
-                    upd_done[cur] = None
-                if peer is not None:
-                    peer.before_slot_write(gi, cur, torch.cuda.current_stream(slot.device))
-                if base_i + self.rank < len(params):
-                    p = params[base_i + self.rank]
-                    g = p.grad
-                    assert g is not None
-                    if grad_ready is not None and p in grad_ready:
-                        torch.cuda.current_stream(g.device).wait_event(grad_ready[p])
-                    state = self.state[p]
-                    if "momentum_buffer" not in state:
-                        state["momentum_buffer"] = torch.zeros_like(g)
-                    buf: Tensor = state["momentum_buffer"]
-                    g = self._momentum(g, buf, group["momentum"], group["nesterov"])
-                    if g.ndim == 4:  # for the case of conv filters
-                        g = g.view(len(g), -1)
-                    self._orthogonalize(g, slot, group["ns_steps"])
-                    if overlap:
-                        ns_done[cur] = torch.cuda.Event()
-                        ns_done[cur].record(main)
-                else:
-                    ns_done[cur] = None
-                # an idle rank contributes whatever its slot holds (muon.py:104-105)
-                if base_i > 0:
-                    update_prev()
-                if peer is not None:
-                    handle = peer.publish(gi, cur, slot, list(range(min(ws, len(params) - base_i))))
-                elif ws > 1:
-                    handle = self._all_gather(buffers[cur], slot)
+                # buffer `cur` always travels on lane `cur`
+                lane = lanes[cur] if lanes is not None else (main if overlap else None)
+                self._lane = cur if lanes is not None else 0
+                with (torch.cuda.stream(lane) if lanes is not None else contextlib.nullcontext()):
+                    if overlap and upd_done[cur] is not None:
+                        lane.wait_event(upd_done[cur])  # buffer `cur` is free to be overwritten
+                        upd_done[cur] = None
+                    if peer is not None:
+                        peer.before_slot_write(gi, cur, torch.cuda.current_stream(slot.device))
+                    if base_i + self.rank < len(params):
+                        p = params[base_i + self.rank]
+                        g = p.grad
+                        assert g is not None
+                        if grad_ready is not None and p in grad_ready:
+                            torch.cuda.current_stream(g.device).wait_event(grad_ready[p])
+                        state = self.state[p]
+                        if "momentum_buffer" not in state:
+                            state["momentum_buffer"] = torch.zeros_like(g)
+                        buf: Tensor = state["momentum_buffer"]
+                        g = self._momentum(g, buf, group["momentum"], group["nesterov"])
+                        if g.ndim == 4:  # for the case of conv filters
+                            g = g.view(len(g), -1)
+                        self._orthogonalize(g, slot, group["ns_steps"])
+                        if overlap:
+                            ns_done[cur] = torch.cuda.Event()
+                            ns_done[cur].record(lane)
+                    else:
+                        ns_done[cur] = None
+                    # an idle rank contributes whatever its slot holds (muon.py:104-105)
+                    if base_i > 0:
+                        update_prev()
+                    if peer is not None:
+                        handle = peer.publish(gi, cur, slot, list(range(min(ws, len(params) - base_i))))
+                    elif ws > 1:
+                        handle = self._all_gather(buffers[cur], slot)
                 params_world = params[base_i: base_i + ws]
                 prev = cur
             if params_world is not None:
                 update_prev()
         if overlap:
             main.wait_stream(side)  # the step's effects are ordered on the caller's stream
+            if lanes is not None:
+                main.wait_stream(lanes[1])
