@@ -52,6 +52,7 @@ sumsq_partial_kernel(const T* __restrict__ g, long long rows, long long cols, lo
   if (vec_ok) {  // contiguous, 16-byte aligned, n % V == 0
     const long long nv = n / V;
     const uint4* g4 = reinterpret_cast<const uint4*>(g);
+#pragma unroll 4
     for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < nv;
          i += (long long)gridDim.x * 256) {
       const uint4 raw = __ldg(g4 + i);
@@ -141,21 +142,29 @@ scale_transpose_vec_kernel(const T* __restrict__ g, long long rows, long long co
   // 16-byte stores and the column-wise gathers below are free of bank conflicts
   __shared__ __align__(16) __nv_bfloat16 tile[64][64];
   auto swz = [](int r, int c) { return (((c >> 3) ^ ((r >> 3) & 7)) << 3) | (c & 7); };
+  const long long tiles_c = cols / 64;
+  const long long tr = blockIdx.x / tiles_c, tc = blockIdx.x - tr * tiles_c;
+  const long long r0 = tr * 64, c0 = tc * 64;
+  constexpr int LOADS = (64 * CHUNKS) / 256;
+  // the tile's loads go out first; folding the partial sums hides under their latency
+  uint4 raw[LOADS];
+#pragma unroll
+  for (int i = 0; i < LOADS; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    const int rr = idx / CHUNKS, cc = (idx % CHUNKS) * V;
+    raw[i] = __ldg(reinterpret_cast<const uint4*>(g + (r0 + rr) * ldg + c0 + cc));
+  }
   float s = 0.f;
   for (int i = threadIdx.x; i < nparts; i += 256) s += partials[i];
   const float total = block_sum_256(s, red);
   const float d = __bfloat162float(__float2bfloat16_rn(sqrtf(total)));
   const float dp = __bfloat162float(__float2bfloat16_rn(d + 1e-7f));
 
-  const long long tiles_c = cols / 64;
-  const long long tr = blockIdx.x / tiles_c, tc = blockIdx.x - tr * tiles_c;
-  const long long r0 = tr * 64, c0 = tc * 64;
 #pragma unroll
-  for (int i = 0; i < (64 * CHUNKS) / 256; ++i) {
+  for (int i = 0; i < LOADS; ++i) {
     const int idx = threadIdx.x + i * 256;
     const int rr = idx / CHUNKS, cc = (idx % CHUNKS) * V;
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(g + (r0 + rr) * ldg + c0 + cc));
-    const T* e = reinterpret_cast<const T*>(&raw);
+    const T* e = reinterpret_cast<const T*>(&raw[i]);
     alignas(16) __nv_bfloat16 q[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) q[j] = __float2bfloat16_rn(as_bf16_value<T>(e[j]) / dp);

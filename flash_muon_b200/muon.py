@@ -118,6 +118,12 @@ class Muon(torch.optim.Optimizer):
 
     def _peer_gather(self):
         """The copy-engine all-gather, set up collectively on first use (None: use NCCL)."""
+        if self._peer:
+            # load_state_dict() replaces the gather buffers: the exported addresses are stale then
+            now = [(g["update_buffer"].data_ptr(), g["update_buffer_alt"].data_ptr())
+                   for g in self.param_groups]
+            if now != self._peer.buffer_ptrs:
+                self._peer = None
         if self._peer is None:
             self._peer = False
             want = os.environ.get("FM_MUON_GATHER", "peer") != "nccl"

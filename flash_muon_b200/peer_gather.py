@@ -75,6 +75,7 @@ class PeerGather:
         self.device = buffers[0][0].device
         self.ngroups = len(buffers)
         self.buffers = buffers
+        self.buffer_ptrs = [(b0.data_ptr(), b1.data_ptr()) for b0, b1 in buffers]
         # [group, buffer, kind, rank] use counters written by peers
         self.flags = torch.zeros(self.ngroups, 2, 2, world_size, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)

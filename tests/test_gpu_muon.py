@@ -154,6 +154,64 @@ def test_streaming_hooks_give_the_same_step():
         assert torch.equal(p, r) and torch.equal(out[p], r.detach().cpu())
 
 
+def test_step_replays_from_a_cuda_graph():
+    """The whole step (three streams, events, ~20 launches per matrix, no allocation after the
+    first step) can be captured once and replayed: same parameters as eager steps."""
+    steps = 3
+    params, grads = muon_case(steps, seed=11)
+    ref, _ = run_product(params, grads, steps, **MUON_HP)
+    ps = [torch.nn.Parameter(p.to(DEV)) for p in params]
+    opt = fm.Muon(ps, rank=0, world_size=1, **MUON_HP)
+    static_g = [torch.zeros_like(p) for p in ps]
+    for p, g in zip(ps, static_g):
+        p.grad = g
+    # step 0 eagerly (creates momentum buffers and workspaces), then capture one step
+    for g, src in zip(static_g, grads[0]):
+        g.copy_(src.to(DEV))
+    opt.step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    cap = torch.cuda.Stream()
+    cap.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(cap):
+        saved = [p.detach().clone() for p in ps]
+        bufs = [opt.state[p]["momentum_buffer"].clone() for p in ps]
+        with torch.cuda.graph(graph, stream=cap):
+            opt.step()
+        # capture does not execute: parameters and momentum are as before
+        for p, s0, b0 in zip(ps, saved, bufs):
+            assert torch.equal(p, s0) and torch.equal(opt.state[p]["momentum_buffer"], b0)
+    torch.cuda.current_stream().wait_stream(cap)
+    for t in range(1, steps):
+        for g, src in zip(static_g, grads[t]):
+            g.copy_(src.to(DEV))
+        graph.replay()
+    torch.cuda.synchronize()
+    for p, r in zip(ps, ref):
+        assert torch.equal(p, r)
+    _lib.device_status()
+
+
+def test_state_dict_round_trip():
+    """momentum_buffer survives state_dict() / load_state_dict() like any torch optimizer state."""
+    params, grads = muon_case(2, seed=12)
+    ref, _ = run_product(params, grads, 2, **MUON_HP)
+    ps = [torch.nn.Parameter(p.to(DEV)) for p in params]
+    opt = fm.Muon(ps, rank=0, world_size=1, **MUON_HP)
+    for p, g in zip(ps, grads[0]):
+        p.grad = g.to(DEV).clone()
+    opt.step()
+    sd = opt.state_dict()
+    opt2 = fm.Muon(ps, rank=0, world_size=1, **MUON_HP)
+    opt2.load_state_dict(sd)
+    for p, g in zip(ps, grads[1]):
+        p.grad = g.to(DEV).clone()
+    opt2.step()
+    torch.cuda.synchronize()
+    for p, r in zip(ps, ref):
+        assert torch.equal(p, r)
+
+
 def test_missing_grad_asserts():
     p = torch.nn.Parameter(torch.randn(32, 32, device=DEV).bfloat16())
     opt = fm.Muon([p], rank=0, world_size=1)
