@@ -7,8 +7,8 @@ What differs is how the device work is issued:
 * momentum + Nesterov is one fused kernel (``fm_momentum``) instead of two ``lerp_`` launches;
 * Newton-Schulz is one C-ABI call whose last GEMM epilogue writes the flat update straight into
   this rank's slot of the gather buffer (no ``.flatten()`` copy, no staging tensor);
-* the gather buffer is double-buffered, so round ``i+1`` may fill its slot while round ``i`` is
-  still being gathered and applied;
+* rounds rotate through four gather buffers, so a round may fill its slot while older rounds
+  are still being gathered and applied;
 * the all-gather (flash_muon/muon.py:106-108) overlaps the next round's Newton-Schulz like the
   reference's ``async_op=True`` call.  Inside one box it is done by DMA copy engines pushing
   each finished slot into the peers' buffers, ordered by stream-side flags
@@ -48,15 +48,13 @@ class Muon(torch.optim.Optimizer):
 
     # Device of the gather buffers ("cuda" = the current CUDA device, flash_muon/muon.py:69).
     _buffer_device = "cuda"
+    _num_buffers = 4
     # Apply the decay + update of a finished round on a second stream, under the next GEMMs.
     _overlap_updates = True
     # Alternate rounds between two streams: the GEMM kernels are persistent and statically
     # scheduled, so a kernel's last wave leaves SMs idle; with an independent matrix in flight on
     # the other stream its CTAs take those SMs.  Needs _overlap_updates (event-ordered rounds).
-    # Measured on the Llama-3-8B shapes: -4 % at 1 and 2 GPUs, -3 % at 4, but +5 % at 8, where a
-    # rank has only 8-12 rounds per group and the deeper pipeline drains more slowly than it
-    # helps -- so it is used up to world_size 4 (None = decide by world size).
-    _two_lanes = None
+    _two_lanes = True
 
     def __init__(self, params, lr=0.02, weight_decay=0.01, momentum=0.95, nesterov=True,
                  ns_steps=5, rank=None, world_size=None):
@@ -71,12 +69,15 @@ class Muon(torch.optim.Optimizer):
         # one group per distinct numel (flash_muon/muon.py:68); sorted so that every rank walks
         # the groups in the same order whatever its hash seed
         for size in sorted({p.numel() for p in params}):
-            b = torch.empty(world_size, size, dtype=torch.bfloat16, device=self._buffer_device)
-            b2 = torch.empty(world_size, size, dtype=torch.bfloat16, device=self._buffer_device)
+            # the reference has one gather buffer per group; rounds here rotate through four
+            # (two per compute stream), so a round never waits for the buffer of an older one
+            bs = [torch.empty(world_size, size, dtype=torch.bfloat16, device=self._buffer_device)
+                  for _ in range(self._num_buffers)]
+            vs = [[b[i] for i in range(world_size)] for b in bs]
             group = dict(params=[p for p in params if p.numel() == size],
-                         update_buffer=b, update_buffer_views=[b[i] for i in range(world_size)],
-                         update_buffer_alt=b2,
-                         update_buffer_alt_views=[b2[i] for i in range(world_size)])
+                         update_buffer=bs[0], update_buffer_views=vs[0],
+                         update_buffer_alt=bs[1], update_buffer_alt_views=vs[1],
+                         update_buffer_more=bs[2:], update_buffer_more_views=vs[2:])
             param_groups.append(group)
         super().__init__(param_groups, defaults)
         self._workspaces: dict = {}   # lane -> Newton-Schulz scratch
@@ -116,12 +117,19 @@ class Muon(torch.optim.Optimizer):
         # in place: `slot` is row `rank` of `buffer`                    (flash_muon/muon.py:108)
         return dist.all_gather_into_tensor(buffer, slot, async_op=True)
 
+    @staticmethod
+    def _group_buffers(group):
+        """(buffers, views) of a group in rotation order."""
+        bufs = [group["update_buffer"], group["update_buffer_alt"], *group["update_buffer_more"]]
+        views = [group["update_buffer_views"], group["update_buffer_alt_views"],
+                 *group["update_buffer_more_views"]]
+        return bufs, views
+
     def _peer_gather(self):
         """The copy-engine all-gather, set up collectively on first use (None: use NCCL)."""
         if self._peer:
             # load_state_dict() replaces the gather buffers: the exported addresses are stale then
-            now = [(g["update_buffer"].data_ptr(), g["update_buffer_alt"].data_ptr())
-                   for g in self.param_groups]
+            now = [[b.data_ptr() for b in self._group_buffers(g)[0]] for g in self.param_groups]
             if now != self._peer.buffer_ptrs:
                 self._peer = None
         if self._peer is None:
@@ -132,8 +140,7 @@ class Muon(torch.optim.Optimizer):
                 ok, peer = 1, None
                 try:
                     peer = PeerGather(self.rank, self.world_size,
-                                      [(g["update_buffer"], g["update_buffer_alt"])
-                                       for g in self.param_groups])
+                                      [self._group_buffers(g)[0] for g in self.param_groups])
                 except Exception as exc:  # same decision on every rank, taken below
                     ok = 0
                     warnings.warn(f"peer all-gather unavailable ({exc}); using NCCL")
@@ -190,22 +197,21 @@ class Muon(torch.optim.Optimizer):
             device = self.param_groups[0]["update_buffer"].device
             main = torch.cuda.current_stream(device)
             side = self._side_stream(device)
-            two = self._two_lanes if self._two_lanes is not None else (ws <= 4)
-            if two:
+            if self._two_lanes:
                 if getattr(self, "_lane1", None) is None or self._lane1.device != device:
                     self._lane1 = torch.cuda.Stream(device=device)
                 lanes = (main, self._lane1)
                 self._lane1.wait_stream(main)   # gradients produced on the caller's stream
         peer = self._peer_gather() if (ws > 1 and type(self)._all_gather is Muon._all_gather) else None
         for gi, group in enumerate(self.param_groups):
-            buffers = (group["update_buffer"], group["update_buffer_alt"])
-            views = (group["update_buffer_views"], group["update_buffer_alt_views"])
+            buffers, views = self._group_buffers(group)
+            nbuf = len(buffers)
             params: list[Tensor] = group["params"]
             handle = None
             params_world = None
             prev = 0                   # which buffer the round in flight uses
-            ns_done = [None, None]     # per buffer: this rank's slot has been written (main stream)
-            upd_done = [None, None]    # per buffer: its updates have been applied (side stream)
+            ns_done = [None] * nbuf    # per buffer: this rank's slot has been written
+            upd_done = [None] * nbuf   # per buffer: its updates have been applied (side stream)
 
             def update_prev():
                 if not overlap:
@@ -233,11 +239,11 @@ class Muon(torch.optim.Optimizer):
                     upd_done[prev].record(side)
 
             for round_idx, base_i in enumerate(range(0, len(params), ws)):
-                cur = round_idx & 1
+                cur = round_idx % nbuf
                 slot = views[cur][self.rank]
-                # buffer `cur` always travels on lane `cur`
-                lane = lanes[cur] if lanes is not None else (main if overlap else None)
-                self._lane = cur if lanes is not None else 0
+                # buffer `cur` always travels on lane `cur % 2`
+                lane = lanes[cur & 1] if lanes is not None else (main if overlap else None)
+                self._lane = (cur & 1) if lanes is not None else 0
                 with (torch.cuda.stream(lane) if lanes is not None else contextlib.nullcontext()):
                     if overlap and upd_done[cur] is not None:
                         lane.wait_event(upd_done[cur])  # buffer `cur` is free to be overwritten

@@ -8,7 +8,8 @@ finished slot into the gather buffers of its peers with DMA copy engines, and th
 ordered by 32-bit flags that the CUDA streams themselves write and wait on
 (``fm_stream_write32`` / ``fm_stream_wait32_geq``): no kernel, no SM, no host synchronisation.
 
-Per numel group there are two gather buffers (double buffering) and, for each, two flag rows:
+Per numel group there are several gather buffers (rounds rotate through them) and, for each, two
+flag rows:
 
 * ``READY[r]`` -- written by producer ``r`` into every consumer after its slot has landed;
 * ``ACK[q]``   -- written by consumer ``q`` into producer ``r`` once ``q`` has applied the update
@@ -68,39 +69,42 @@ class PeerRound:
 
 class PeerGather:
     """Collective constructor: every rank of the default group must call it with the same list of
-    ``(buffer, alt_buffer)`` pairs (one per numel group, ``[world_size, numel]`` bf16 each)."""
+    buffer lists (one list per numel group, ``[world_size, numel]`` bf16 each, the same number of
+    buffers in every group)."""
 
-    def __init__(self, rank: int, world_size: int, buffers: list[tuple[torch.Tensor, torch.Tensor]]):
+    def __init__(self, rank: int, world_size: int, buffers: list[list[torch.Tensor]]):
         self.rank, self.ws = rank, world_size
         self.device = buffers[0][0].device
         self.ngroups = len(buffers)
+        self.nbuf = len(buffers[0])
         self.buffers = buffers
-        self.buffer_ptrs = [(b0.data_ptr(), b1.data_ptr()) for b0, b1 in buffers]
+        self.buffer_ptrs = [[b.data_ptr() for b in bl] for bl in buffers]
         # [group, buffer, kind, rank] use counters written by peers
-        self.flags = torch.zeros(self.ngroups, 2, 2, world_size, dtype=torch.int32, device=self.device)
+        self.flags = torch.zeros(self.ngroups, self.nbuf, 2, world_size, dtype=torch.int32,
+                                 device=self.device)
         torch.cuda.synchronize(self.device)
         mine = {"flags": _export(self.flags),
-                "bufs": [(_export(b0), _export(b1)) for b0, b1 in buffers]}
+                "bufs": [[_export(b) for b in bl] for bl in buffers]}
         everyone: list = [None] * world_size
         dist.all_gather_object(everyone, mine)
         self._flag_base = [0] * world_size
-        self._buf_base = [[(0, 0)] * self.ngroups for _ in range(world_size)]
+        self._buf_base = [None] * world_size
         for r, info in enumerate(everyone):
             if r == rank:
                 self._flag_base[r] = self.flags.data_ptr()
-                self._buf_base[r] = [(b0.data_ptr(), b1.data_ptr()) for b0, b1 in buffers]
+                self._buf_base[r] = self.buffer_ptrs
             else:
                 self._flag_base[r] = _import(*info["flags"])
-                self._buf_base[r] = [(_import(*h0), _import(*h1)) for h0, h1 in info["bufs"]]
+                self._buf_base[r] = [[_import(*h) for h in hl] for hl in info["bufs"]]
         dist.barrier()  # nobody writes a flag before everybody has zeroed and mapped them
         self.streams = {q: torch.cuda.Stream(device=self.device) for q in range(world_size) if q != rank}
         # host-side mirror of the use counters: seq[group][buffer][producer]
-        self.seq = [[[0] * world_size for _ in range(2)] for _ in range(self.ngroups)]
+        self.seq = [[[0] * world_size for _ in range(self.nbuf)] for _ in range(self.ngroups)]
         # events of this rank's copies out of its slot, per (group, buffer)
-        self.push_events = [[[], []] for _ in range(self.ngroups)]
+        self.push_events = [[[] for _ in range(self.nbuf)] for _ in range(self.ngroups)]
 
     def flag_addr(self, holder: int, gi: int, b: int, kind: int, idx: int) -> int:
-        return self._flag_base[holder] + 4 * ((((gi * 2 + b) * 2 + kind) * self.ws) + idx)
+        return self._flag_base[holder] + 4 * ((((gi * self.nbuf + b) * 2 + kind) * self.ws) + idx)
 
     def before_slot_write(self, gi: int, b: int, stream: torch.cuda.Stream) -> None:
         """``stream`` is about to overwrite this rank's slot of buffer ``b``: earlier copies out
