@@ -62,10 +62,12 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.proc, self.path = index, None, None
+    def __init__(self, index: int, enabled: bool = True):
+        self.index, self.proc, self.path, self.enabled = index, None, None, enabled
 
     def __enter__(self):
+        if not self.enabled:
+            return self
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -247,7 +249,7 @@ def run_ours(args):
     # ---- device-resident leg: gradients already in HBM.  Clock samples cover the warm-up steps
     # as well (same load), so that short timed regions still get several samples.
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clk:
+    with ClockSampler(local, enabled=(rank == 0)) as clk:
         for _ in range(args.warmup):
             opt.step()
         sync()

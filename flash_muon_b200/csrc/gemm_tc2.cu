@@ -175,9 +175,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t leader_full = ptx::mapa(full_bar(s), 0);
-          if (rank == 0) ptx::mbar_expect_tx(full_bar(s), 4u * kSlabBytes);  // both CTAs' slabs
+          // On a diagonal tile of the symmetric product the B slab is the A slab (same rows of
+          // the same matrix): load it once and let the MMA read it through both descriptors.
+          const bool same = p.sym && (tl.m0 == tl.n0);
+          if (rank == 0) ptx::mbar_expect_tx(full_bar(s), (same ? 2u : 4u) * kSlabBytes);
           ptx::tma_load_2d_pair(a_smem(s), &tmA, leader_full, kb * BK, tl.m0 + (int)rank * 128);
-          ptx::tma_load_2d_pair(b_smem(s), &tmB, leader_full, kb * BK, tl.n0 + (int)rank * 128);
+          if (!same)
+            ptx::tma_load_2d_pair(b_smem(s), &tmB, leader_full, kb * BK, tl.n0 + (int)rank * 128);
           if (first) { FM_TRACE_MARK(p, 2); first = false; }
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
@@ -199,12 +203,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (!ptx::mbar_wait_cluster(tempty_bar(acc), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
+        const Tile2 tl = decode_tile2(p, w.tile);
+        const bool same = p.sym && (tl.m0 == tl.n0);
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
           if (kb == w.kb0) FM_TRACE_MARK(p, 3);
           ptx::tc_fence_after();
           const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_smem(s));
-          const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_smem(s));
+          const uint64_t b_desc = same ? a_desc : ptx::make_kmajor_sw128_desc(b_smem(s));
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             ptx::umma_f16_pair(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
