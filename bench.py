@@ -200,7 +200,7 @@ def time_syrk(peaks, dim=SYRK_DIM, reps=30):
            "tflops_algorithmic": alg / t / 1e9, "tflops_executed": execd / t / 1e9,
            "cublas_ms": tc, "speedup_vs_cublas": tc / t, "reps": reps}
     # DRAM bytes of one 8192^2 launch from an ncu capture (profiles/gemm_tc2_kernel_syrk_8192_bf16.md)
-    traffic = 682.5e6 + 116.6e6 if m == 8192 else None
+    traffic = 692.8e6 + 131.2e6 if m == 8192 else None
     roof = {"kernel": f"gemm_tc2_kernel<bf16> as matmul_transpose {m}x{k}", "bound": "tensor",
             "achieved": alg / t / 1e9, "peak": peaks["bf16"], "unit": "TFLOP/s",
             "frac": alg / t / 1e9 / peaks["bf16"], "frac_executed": execd / t / 1e9 / peaks["bf16"],
