@@ -198,7 +198,21 @@ extern "C" int fm_newtonschulz(const void* G, int64_t rows, int64_t cols, int64_
       a.CT = Bm; a.ldt_r = L.ldm; a.ldt_c = 1;
       if ((rc = gemm_tc(a, st)) != FM_OK) return rc;
     }
-    {  // X' = a*X + B X  (and its transpose)         (muon.py:29)
+    if (last && tall) {
+      // Last step of a tall input: only X'^T = a*X^T + X^T B is wanted (B is symmetric), and in
+      // that orientation it is the direct, 16-byte-store output.  Same products summed in the
+      // same order as B X, so the values are those of the other orientation.
+      GemmArgs a;
+      a.dtype = FM_BF16;
+      a.A = XT[cur]; a.lda = L.ldm;
+      a.B = Bm; a.ldb = L.ldm;
+      a.M = k; a.N = m; a.K = m;
+      a.sym = 0;
+      a.D = XT[cur]; a.ldd = L.ldm;
+      a.alpha = ca; a.beta = 1.f; a.precise = precise;
+      a.C = out; a.ldc_r = cols; a.ldc_c = 1;         // out [rows=k, cols=m]
+      if ((rc = gemm_tc(a, st)) != FM_OK) return rc;
+    } else {  // X' = a*X + B X  (and its transpose)  (muon.py:29)
       GemmArgs a;
       a.dtype = FM_BF16;
       a.A = Bm; a.lda = L.ldm;
@@ -210,10 +224,8 @@ extern "C" int fm_newtonschulz(const void* G, int64_t rows, int64_t cols, int64_
       if (!last) {
         a.C = X[cur ^ 1]; a.ldc_r = L.ldk; a.ldc_c = 1;
         a.CT = XT[cur ^ 1]; a.ldt_r = L.ldm; a.ldt_c = 1;
-      } else if (!tall) {
-        a.C = out; a.ldc_r = cols; a.ldc_c = 1;       // out [rows=m, cols=k]
       } else {
-        a.CT = out; a.ldt_r = cols; a.ldt_c = 1;      // out [rows=k, cols=m] = X'^T
+        a.C = out; a.ldc_r = cols; a.ldc_c = 1;       // out [rows=m, cols=k]
       }
       if ((rc = gemm_tc(a, st)) != FM_OK) return rc;
     }
