@@ -48,13 +48,15 @@ class Muon(torch.optim.Optimizer):
 
     # Device of the gather buffers ("cuda" = the current CUDA device, flash_muon/muon.py:69).
     _buffer_device = "cuda"
-    _num_buffers = 4
     # Apply the decay + update of a finished round on a second stream, under the next GEMMs.
     _overlap_updates = True
-    # Alternate rounds between two streams: the GEMM kernels are persistent and statically
-    # scheduled, so a kernel's last wave leaves SMs idle; with an independent matrix in flight on
-    # the other stream its CTAs take those SMs.  Needs _overlap_updates (event-ordered rounds).
-    _two_lanes = True
+    # Rounds rotate over several streams ("lanes"): the GEMM kernels are persistent and
+    # statically scheduled, so a kernel's last wave leaves SMs idle, and a matrix with
+    # min(rows, cols) <= 1024 fills at most 36 of 148 SMs; independent matrices in flight on
+    # other streams take the idle SMs.  Two lanes for large matrices, four for small ones, two
+    # gather buffers per lane.  Needs _overlap_updates (event-ordered rounds).
+    _two_lanes = True          # False: a single compute stream
+    _small_dim = 1536          # groups whose matrices are all at most this narrow get 4 lanes
 
     def __init__(self, params, lr=0.02, weight_decay=0.01, momentum=0.95, nesterov=True,
                  ns_steps=5, rank=None, world_size=None):
@@ -69,12 +71,15 @@ class Muon(torch.optim.Optimizer):
         # one group per distinct numel (flash_muon/muon.py:68); sorted so that every rank walks
         # the groups in the same order whatever its hash seed
         for size in sorted({p.numel() for p in params}):
-            # the reference has one gather buffer per group; rounds here rotate through four
-            # (two per compute stream), so a round never waits for the buffer of an older one
+            # the reference has one gather buffer per group; rounds here rotate through two per
+            # compute stream, so a round never waits for the buffer of an older one
+            members = [p for p in params if p.numel() == size]
+            narrow = max(min(p.size(0), p.numel() // max(p.size(0), 1)) for p in members)
+            lanes = 4 if narrow <= self._small_dim else 2
             bs = [torch.empty(world_size, size, dtype=torch.bfloat16, device=self._buffer_device)
-                  for _ in range(self._num_buffers)]
+                  for _ in range(2 * lanes)]
             vs = [[b[i] for i in range(world_size)] for b in bs]
-            group = dict(params=[p for p in params if p.numel() == size],
+            group = dict(params=members, lanes=lanes,
                          update_buffer=bs[0], update_buffer_views=vs[0],
                          update_buffer_alt=bs[1], update_buffer_alt_views=vs[1],
                          update_buffer_more=bs[2:], update_buffer_more_views=vs[2:])
@@ -86,18 +91,12 @@ class Muon(torch.optim.Optimizer):
 
     # ------------------------------------------------------------------ helpers
     def _ns_workspace(self, rows: int, cols: int, device) -> Tensor:
-        """Newton-Schulz scratch of the lane (stream) the current round runs on."""
+        """Newton-Schulz scratch of the lane (stream) the current round runs on; grows to the
+        largest matrix that lane has seen (groups are visited in order of size)."""
         need = newtonschulz_workspace_bytes(rows, cols)
         ws = self._workspaces.get(self._lane)
         if ws is None or ws.numel() < need or ws.device != device:
-            # sized once for the largest matrix this rank owns
-            biggest = need
-            for group in self.param_groups:
-                for i, p in enumerate(group["params"]):
-                    if i % self.world_size == self.rank and p.ndim >= 2:
-                        r = p.size(0)
-                        biggest = max(biggest, newtonschulz_workspace_bytes(r, p.numel() // r))
-            self._workspaces[self._lane] = ws = torch.empty(biggest, dtype=torch.uint8, device=device)
+            self._workspaces[self._lane] = ws = torch.empty(need, dtype=torch.uint8, device=device)
         return ws
 
     def _momentum(self, g: Tensor, buf: Tensor, momentum: float, nesterov: bool) -> Tensor:
@@ -198,10 +197,12 @@ class Muon(torch.optim.Optimizer):
             main = torch.cuda.current_stream(device)
             side = self._side_stream(device)
             if self._two_lanes:
-                if getattr(self, "_lane1", None) is None or self._lane1.device != device:
-                    self._lane1 = torch.cuda.Stream(device=device)
-                lanes = (main, self._lane1)
-                self._lane1.wait_stream(main)   # gradients produced on the caller's stream
+                extra = getattr(self, "_extra_lanes", None)
+                if extra is None or extra[0].device != device:
+                    self._extra_lanes = extra = [torch.cuda.Stream(device=device) for _ in range(3)]
+                lanes = (main, *extra)
+                for st in extra:
+                    st.wait_stream(main)        # gradients produced on the caller's stream
         peer = self._peer_gather() if (ws > 1 and type(self)._all_gather is Muon._all_gather) else None
         for gi, group in enumerate(self.param_groups):
             buffers, views = self._group_buffers(group)
@@ -241,9 +242,10 @@ class Muon(torch.optim.Optimizer):
             for round_idx, base_i in enumerate(range(0, len(params), ws)):
                 cur = round_idx % nbuf
                 slot = views[cur][self.rank]
-                # buffer `cur` always travels on lane `cur % 2`
-                lane = lanes[cur & 1] if lanes is not None else (main if overlap else None)
-                self._lane = (cur & 1) if lanes is not None else 0
+                # buffer `cur` always travels on lane `cur % nlanes`
+                nlanes = group.get("lanes", 2)
+                lane = lanes[cur % nlanes] if lanes is not None else (main if overlap else None)
+                self._lane = (cur % nlanes) if lanes is not None else 0
                 with (torch.cuda.stream(lane) if lanes is not None else contextlib.nullcontext()):
                     if overlap and upd_done[cur] is not None:
                         lane.wait_event(upd_done[cur])  # buffer `cur` is free to be overwritten
@@ -283,4 +285,5 @@ class Muon(torch.optim.Optimizer):
         if overlap:
             main.wait_stream(side)  # the step's effects are ordered on the caller's stream
             if lanes is not None:
-                main.wait_stream(lanes[1])
+                for st in lanes[1:]:
+                    main.wait_stream(st)

@@ -69,14 +69,13 @@ class PeerRound:
 
 class PeerGather:
     """Collective constructor: every rank of the default group must call it with the same list of
-    buffer lists (one list per numel group, ``[world_size, numel]`` bf16 each, the same number of
-    buffers in every group)."""
+    buffer lists (one list per numel group, ``[world_size, numel]`` bf16 each)."""
 
     def __init__(self, rank: int, world_size: int, buffers: list[list[torch.Tensor]]):
         self.rank, self.ws = rank, world_size
         self.device = buffers[0][0].device
         self.ngroups = len(buffers)
-        self.nbuf = len(buffers[0])
+        self.nbuf = max(len(bl) for bl in buffers)
         self.buffers = buffers
         self.buffer_ptrs = [[b.data_ptr() for b in bl] for bl in buffers]
         # [group, buffer, kind, rank] use counters written by peers
