@@ -57,6 +57,7 @@ class Muon(torch.optim.Optimizer):
     # gather buffers per lane.  Needs _overlap_updates (event-ordered rounds).
     _two_lanes = True          # False: a single compute stream
     _small_dim = 1536          # groups whose matrices are all at most this narrow get 4 lanes
+    _large_lanes = 2           # lanes of the other groups
 
     def __init__(self, params, lr=0.02, weight_decay=0.01, momentum=0.95, nesterov=True,
                  ns_steps=5, rank=None, world_size=None):
@@ -75,7 +76,7 @@ class Muon(torch.optim.Optimizer):
             # compute stream, so a round never waits for the buffer of an older one
             members = [p for p in params if p.numel() == size]
             narrow = max(min(p.size(0), p.numel() // max(p.size(0), 1)) for p in members)
-            lanes = 4 if narrow <= self._small_dim else 2
+            lanes = 4 if narrow <= self._small_dim else self._large_lanes
             bs = [torch.empty(world_size, size, dtype=torch.bfloat16, device=self._buffer_device)
                   for _ in range(2 * lanes)]
             vs = [[b[i] for i in range(world_size)] for b in bs]

@@ -60,6 +60,15 @@ def test_host_only_calls():
     assert lib.fm_newtonschulz(None, 4, 4, 4, 0, 5, None, None, 0, 0, None) == -1
     assert lib.fm_momentum(None, None, 4, 0, 0.95, 1, None) == -1
     assert lib.fm_update_multi(None, None, None, None, -1, 0, 1.0, None) == -1
+    assert lib.fm_newtonschulz_static(None, 0, 4, 4, 0, 5, None, 0, None) == -1
+    assert lib.fm_newtonschulz_static(None, 2048, 2048, 2048, 0, 5, None, 0, None) == -5
+    assert b"1024 x 4096" in lib.fm_last_error()
+    assert lib.fm_ipc_export(None, None, None) == -1
+    assert lib.fm_ipc_import(None, 0, None) == -1
+    assert lib.fm_stream_write32(None, 1, None) == -1
+    assert lib.fm_stream_wait32_geq(None, 1, None) == -1
+    assert lib.fm_copy_async(None, None, 0, None) == 0      # nothing to copy
+    assert lib.fm_copy_async(None, None, 16, None) == -1
 
 
 def test_missing_library_fails_loudly(tmp_path, monkeypatch):

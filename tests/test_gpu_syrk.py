@@ -72,11 +72,17 @@ ODD = [(1, 8), (7, 8), (8, 1), (100, 72), (129, 64), (257, 136), (130, 1000), (3
        (384, 320), (640, 64), (1000, 520)]
 
 
-@pytest.mark.parametrize("bn", ["128", "256"])
+@pytest.mark.parametrize("bn", ["128", "256", "pair"])
 @pytest.mark.parametrize("m,k", ODD)
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
 def test_sizes_off_the_tile_grid(m, k, dt, bn, monkeypatch):
-    monkeypatch.setenv("FM_GEMM_BN", bn)
+    """Every tile shape of the tensor-core family (single CTA 128x128 / 128x256, CTA pair
+    256x256) on sizes that are not multiples of any of them."""
+    if bn == "pair":
+        monkeypatch.setenv("FM_GEMM_IMPL", "2")
+    else:
+        monkeypatch.setenv("FM_GEMM_IMPL", "1")
+        monkeypatch.setenv("FM_GEMM_BN", bn)
     x = torch.randn(m, k, device=DEV, generator=torch.Generator(device=DEV).manual_seed(m * k)).to(dt)
     y = torch.full((m, m), float("nan"), device=DEV, dtype=dt)  # canary: every element written
     fm.matmul_transpose_assign(x, y)
