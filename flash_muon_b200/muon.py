@@ -136,11 +136,13 @@ class Muon(torch.optim.Optimizer):
             self._peer = False
             want = os.environ.get("FM_MUON_GATHER", "peer") != "nccl"
             if want and self.world_size > 1 and self.param_groups[0]["update_buffer"].is_cuda:
-                from .peer_gather import PeerGather
+                from .peer_gather import CudaOps, PeerGather
                 ok, peer = 1, None
                 try:
+                    device = self.param_groups[0]["update_buffer"].device
                     peer = PeerGather(self.rank, self.world_size,
-                                      [self._group_buffers(g)[0] for g in self.param_groups])
+                                      [[b.data_ptr() for b in self._group_buffers(g)[0]]
+                                       for g in self.param_groups], CudaOps(device))
                 except Exception as exc:  # same decision on every rank, taken below
                     ok = 0
                     warnings.warn(f"peer all-gather unavailable ({exc}); using NCCL")
@@ -276,7 +278,8 @@ class Muon(torch.optim.Optimizer):
                     if base_i > 0:
                         update_prev()
                     if peer is not None:
-                        handle = peer.publish(gi, cur, slot, list(range(min(ws, len(params) - base_i))))
+                        handle = peer.publish(gi, cur, slot.data_ptr(), slot.numel() * slot.element_size(),
+                                              list(range(min(ws, len(params) - base_i))))
                     elif ws > 1:
                         handle = self._all_gather(buffers[cur], slot)
                 params_world = params[base_i: base_i + ws]

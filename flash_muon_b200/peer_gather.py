@@ -19,6 +19,10 @@ Flag values are per-(producer, buffer) use counters that every rank advances ide
 value is ever reused and a late flag can never be mistaken for an early one.
 Process-to-process addresses come from CUDA IPC handles exchanged once through the existing
 ``torch.distributed`` group.
+
+All device-facing operations go through a small ``ops`` object (``CudaOps`` here); the protocol
+itself is plain bookkeeping, which lets a test drive it against simulated streams under
+arbitrary interleavings.
 """
 from __future__ import annotations
 
@@ -32,71 +36,112 @@ from ._lib import check, lib
 READY, ACK = 0, 1
 
 
-def _export(t: torch.Tensor):
-    handle = ctypes.create_string_buffer(64)
-    off = ctypes.c_uint64(0)
-    check(lib.fm_ipc_export(t.data_ptr(), handle, ctypes.byref(off)))
-    return handle.raw, off.value
+class CudaOps:
+    """The device operations the protocol needs, on real CUDA streams of one device."""
 
+    def __init__(self, device: torch.device):
+        self.device = device
 
-def _import(handle: bytes, offset: int) -> int:
-    out = ctypes.c_void_p(0)
-    check(lib.fm_ipc_import(handle, offset, ctypes.byref(out)))
-    return out.value
+    # -- set-up (collective)
+    def alloc_flags(self, n: int):
+        t = torch.zeros(n, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        return t, t.data_ptr()
+
+    def export(self, addr: int) -> tuple:
+        handle = ctypes.create_string_buffer(64)
+        off = ctypes.c_uint64(0)
+        check(lib.fm_ipc_export(addr, handle, ctypes.byref(off)))
+        return handle.raw, off.value
+
+    def import_(self, exported: tuple) -> int:
+        out = ctypes.c_void_p(0)
+        check(lib.fm_ipc_import(exported[0], exported[1], ctypes.byref(out)))
+        return out.value
+
+    def exchange(self, obj, world_size: int) -> list:
+        everyone: list = [None] * world_size
+        dist.all_gather_object(everyone, obj)
+        return everyone
+
+    def barrier(self) -> None:
+        dist.barrier()
+
+    # -- streams and events
+    def new_stream(self):
+        return torch.cuda.Stream(device=self.device)
+
+    def current_stream(self):
+        return torch.cuda.current_stream(self.device)
+
+    def record(self, stream):
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        return ev
+
+    def wait_event(self, stream, event) -> None:
+        stream.wait_event(event)
+
+    # -- stream-ordered memory operations
+    def wait32_geq(self, stream, addr: int, value: int) -> None:
+        check(lib.fm_stream_wait32_geq(addr, value, stream.cuda_stream))
+
+    def write32(self, stream, addr: int, value: int) -> None:
+        check(lib.fm_stream_write32(addr, value, stream.cuda_stream))
+
+    def copy(self, stream, dst: int, src: int, nbytes: int) -> None:
+        check(lib.fm_copy_async(dst, src, nbytes, stream.cuda_stream))
 
 
 class PeerRound:
     """What ``Muon.step`` holds for a round in flight: ``wait()`` before the update reads the
-    buffer, ``done()`` after it has."""
+    buffer, ``done()`` after it has (both on the stream that is current at the call)."""
 
     def __init__(self, owner: "PeerGather", gi: int, b: int, producers: list[int], seqs: list[int]):
         self.owner, self.gi, self.b, self.producers, self.seqs = owner, gi, b, producers, seqs
 
     def wait(self) -> None:
         o = self.owner
-        st = torch.cuda.current_stream(o.device).cuda_stream
+        st = o.ops.current_stream()
         for r, s in zip(self.producers, self.seqs):
             if r != o.rank:
-                check(lib.fm_stream_wait32_geq(o.flag_addr(o.rank, self.gi, self.b, READY, r), s, st))
+                o.ops.wait32_geq(st, o.flag_addr(o.rank, self.gi, self.b, READY, r), s)
 
     def done(self) -> None:
         o = self.owner
-        st = torch.cuda.current_stream(o.device).cuda_stream
+        st = o.ops.current_stream()
         for r, s in zip(self.producers, self.seqs):
             if r != o.rank:
-                check(lib.fm_stream_write32(o.flag_addr(r, self.gi, self.b, ACK, o.rank), s, st))
+                o.ops.write32(st, o.flag_addr(r, self.gi, self.b, ACK, o.rank), s)
 
 
 class PeerGather:
-    """Collective constructor: every rank of the default group must call it with the same list of
-    buffer lists (one list per numel group, ``[world_size, numel]`` bf16 each)."""
+    """Collective constructor: every rank must call it with the same structure of buffers.
 
-    def __init__(self, rank: int, world_size: int, buffers: list[list[torch.Tensor]]):
-        self.rank, self.ws = rank, world_size
-        self.device = buffers[0][0].device
-        self.ngroups = len(buffers)
-        self.nbuf = max(len(bl) for bl in buffers)
-        self.buffers = buffers
-        self.buffer_ptrs = [[b.data_ptr() for b in bl] for bl in buffers]
+    ``buffer_addrs[g][b]`` is the device address of buffer ``b`` of numel group ``g`` (each
+    ``[world_size, numel]``, rows contiguous) on this rank."""
+
+    def __init__(self, rank: int, world_size: int, buffer_addrs: list[list[int]], ops):
+        self.rank, self.ws, self.ops = rank, world_size, ops
+        self.ngroups = len(buffer_addrs)
+        self.nbuf = max(len(bl) for bl in buffer_addrs)
+        self.buffer_ptrs = [list(bl) for bl in buffer_addrs]
         # [group, buffer, kind, rank] use counters written by peers
-        self.flags = torch.zeros(self.ngroups, self.nbuf, 2, world_size, dtype=torch.int32,
-                                 device=self.device)
-        torch.cuda.synchronize(self.device)
-        mine = {"flags": _export(self.flags),
-                "bufs": [[_export(b) for b in bl] for bl in buffers]}
-        everyone: list = [None] * world_size
-        dist.all_gather_object(everyone, mine)
+        self._flags_keepalive, flag_addr = ops.alloc_flags(self.ngroups * self.nbuf * 2 * world_size)
+        mine = {"flags": ops.export(flag_addr),
+                "bufs": [[ops.export(a) for a in bl] for bl in buffer_addrs]}
+        everyone = ops.exchange(mine, world_size)
         self._flag_base = [0] * world_size
         self._buf_base = [None] * world_size
         for r, info in enumerate(everyone):
             if r == rank:
-                self._flag_base[r] = self.flags.data_ptr()
+                self._flag_base[r] = flag_addr
                 self._buf_base[r] = self.buffer_ptrs
             else:
-                self._flag_base[r] = _import(*info["flags"])
-                self._buf_base[r] = [[_import(*h) for h in hl] for hl in info["bufs"]]
-        dist.barrier()  # nobody writes a flag before everybody has zeroed and mapped them
-        self.streams = {q: torch.cuda.Stream(device=self.device) for q in range(world_size) if q != rank}
+                self._flag_base[r] = ops.import_(info["flags"])
+                self._buf_base[r] = [[ops.import_(h) for h in hl] for hl in info["bufs"]]
+        ops.barrier()  # nobody writes a flag before everybody has zeroed and mapped them
+        self.streams = {q: ops.new_stream() for q in range(world_size) if q != rank}
         # host-side mirror of the use counters: seq[group][buffer][producer]
         self.seq = [[[0] * world_size for _ in range(self.nbuf)] for _ in range(self.ngroups)]
         # events of this rank's copies out of its slot, per (group, buffer)
@@ -105,37 +150,31 @@ class PeerGather:
     def flag_addr(self, holder: int, gi: int, b: int, kind: int, idx: int) -> int:
         return self._flag_base[holder] + 4 * ((((gi * self.nbuf + b) * 2 + kind) * self.ws) + idx)
 
-    def before_slot_write(self, gi: int, b: int, stream: torch.cuda.Stream) -> None:
+    def before_slot_write(self, gi: int, b: int, stream) -> None:
         """``stream`` is about to overwrite this rank's slot of buffer ``b``: earlier copies out
         of it must have finished."""
         for ev in self.push_events[gi][b]:
-            stream.wait_event(ev)
+            self.ops.wait_event(stream, ev)
         self.push_events[gi][b] = []
 
-    def publish(self, gi: int, b: int, slot: torch.Tensor, producers: list[int]) -> PeerRound:
-        """Called on the stream that produced ``slot`` (this rank's row of buffer ``b``)."""
+    def publish(self, gi: int, b: int, slot_addr: int, nbytes: int, producers: list[int]) -> PeerRound:
+        """Called on the stream that produced the slot at ``slot_addr`` (this rank's row of
+        buffer ``b``, ``nbytes`` long)."""
         seqs = []
         for r in producers:
             self.seq[gi][b][r] += 1
             seqs.append(self.seq[gi][b][r])
         if self.rank in producers:
             s = self.seq[gi][b][self.rank]
-            nbytes = slot.numel() * slot.element_size()
-            ready = torch.cuda.Event()
-            ready.record(torch.cuda.current_stream(self.device))
+            ready = self.ops.record(self.ops.current_stream())
             for q, st in self.streams.items():
-                st.wait_event(ready)
-                sp = st.cuda_stream
+                self.ops.wait_event(st, ready)
                 # q has applied the update that read my previous slot in its buffer b
-                check(lib.fm_stream_wait32_geq(self.flag_addr(self.rank, gi, b, ACK, q), s - 1, sp))
-                dst = self._buf_base[q][gi][b] + self.rank * nbytes
-                check(lib.fm_copy_async(dst, slot.data_ptr(), nbytes, sp))
-                check(lib.fm_stream_write32(self.flag_addr(q, gi, b, READY, self.rank), s, sp))
-                ev = torch.cuda.Event()
-                ev.record(st)
-                self.push_events[gi][b].append(ev)
+                self.ops.wait32_geq(st, self.flag_addr(self.rank, gi, b, ACK, q), s - 1)
+                self.ops.copy(st, self._buf_base[q][gi][b] + self.rank * nbytes, slot_addr, nbytes)
+                self.ops.write32(st, self.flag_addr(q, gi, b, READY, self.rank), s)
+                self.push_events[gi][b].append(self.ops.record(st))
         return PeerRound(self, gi, b, producers, seqs)
 
     def close(self) -> None:
-        torch.cuda.synchronize(self.device)
         lib.fm_ipc_close_all()

@@ -1,0 +1,229 @@
+"""The flag protocol of the copy-engine all-gather (flash_muon_b200/peer_gather.py) under a
+simulated set of CUDA streams: every rank's streams are queues of operations that a scheduler
+executes in random order whenever their waits are satisfied.  The simulation checks what no GPU
+run can show exhaustively -- that for every interleaving the protocol neither deadlocks, nor lets
+a consumer read a slot before it has landed, nor lets a producer overwrite a slot (its own or a
+peer's copy of it) that someone still has to read."""
+import random
+
+import pytest
+
+from flash_muon_b200.peer_gather import PeerGather
+
+
+class Sim:
+    """Shared world: memory words, streams of all ranks, exchange board."""
+
+    def __init__(self, world_size, seed):
+        self.ws = world_size
+        self.mem = {}            # address -> int (flags) or ("slot", producer, round) payloads
+        self.streams = []        # all SimStream objects
+        self.board = {}
+        self.rng = random.Random(seed)
+        self.next_addr = 1 << 20
+
+    def alloc(self, nbytes):
+        a = self.next_addr
+        self.next_addr += (nbytes + 255) // 256 * 256 + 256
+        return a
+
+    def run(self):
+        while True:
+            ready = [s for s in self.streams if s.queue and s.queue[0].ready()]
+            if not ready:
+                break
+            s = self.rng.choice(ready)
+            s.queue.pop(0).run()
+        stuck = [s.name for s in self.streams if s.queue]
+        assert not stuck, f"deadlock: streams with pending work {stuck}"
+
+
+class Op:
+    def __init__(self, ready, run):
+        self.ready, self.run = ready, run
+
+
+class SimStream:
+    def __init__(self, sim, name):
+        self.sim, self.name, self.queue = sim, name, []
+        sim.streams.append(self)
+
+    def push(self, ready, run):
+        self.queue.append(Op(ready, run))
+
+
+class SimEvent:
+    def __init__(self):
+        self.done = False
+
+
+class SimOps:
+    """Same interface as peer_gather.CudaOps; addresses are keys of Sim.mem."""
+
+    def __init__(self, sim, rank):
+        self.sim, self.rank = sim, rank
+        self.cur = SimStream(sim, f"r{rank}.main")
+
+    def alloc_flags(self, n):
+        a = self.sim.alloc(4 * n)
+        for i in range(n):
+            self.sim.mem[a + 4 * i] = 0
+        return None, a
+
+    def export(self, addr):
+        return ("h", addr)
+
+    def import_(self, exported):
+        return exported[1]          # one address space in the simulation
+
+    def exchange(self, obj, world_size):
+        self.sim.board[self.rank] = obj
+        return None                 # filled in by the test once every rank has posted
+
+    def barrier(self):
+        pass
+
+    def new_stream(self):
+        return SimStream(self.sim, f"r{self.rank}.s{len(self.sim.streams)}")
+
+    def current_stream(self):
+        return self.cur
+
+    def record(self, stream):
+        ev = SimEvent()
+        stream.push(lambda: True, lambda: setattr(ev, "done", True))
+        return ev
+
+    def wait_event(self, stream, event):
+        stream.push(lambda: event.done, lambda: None)
+
+    def wait32_geq(self, stream, addr, value):
+        stream.push(lambda: self.sim.mem[addr] >= value, lambda: None)
+
+    def write32(self, stream, addr, value):
+        stream.push(lambda: True, lambda: self.sim.mem.__setitem__(addr, value))
+
+    def copy(self, stream, dst, src, nbytes):
+        def run():
+            payload = self.sim.mem[src]
+            old = self.sim.mem.get(dst)
+            # the slot being overwritten must have been consumed by its holder
+            assert old is None or old[3], f"slot {dst} overwritten before it was read: {old}"
+            self.sim.mem[dst] = (payload[0], payload[1], payload[2], False)
+        stream.push(lambda: True, run)
+
+
+def build_world(ws, nbuf, numel_bytes, seed):
+    sim = Sim(ws, seed)
+    opses = [SimOps(sim, r) for r in range(ws)]
+    bufs = [[sim.alloc(ws * numel_bytes) for _ in range(nbuf)] for _ in range(ws)]
+    # PeerGather's constructor is collective: post every rank's exports first, then construct
+    gathers = []
+    # phase 1: flags + exports per rank (mimic the constructor's first half)
+    posted = {}
+    for r, ops in enumerate(opses):
+        keep, fa = ops.alloc_flags(1 * nbuf * 2 * ws)
+        posted[r] = {"flags": ops.export(fa), "bufs": [[ops.export(a) for a in bufs[r]]]}
+        ops._prealloc = (keep, fa)
+    for r, ops in enumerate(opses):
+        ops.alloc_flags = lambda n, o=ops: o._prealloc
+        ops.exchange = lambda obj, w, p=posted: [p[i] for i in range(w)]
+        gathers.append(PeerGather(r, ws, [bufs[r]], ops))
+    return sim, opses, bufs, gathers
+
+
+@pytest.mark.parametrize("ws,nbuf,lanes", [(2, 2, 1), (3, 4, 2), (4, 8, 4), (3, 2, 1)])
+@pytest.mark.parametrize("seed", range(12))
+def test_protocol_is_safe_under_any_interleaving(ws, nbuf, lanes, seed):
+    drive(ws, nbuf, lanes, seed)
+
+
+def test_simulation_catches_a_protocol_without_acknowledgements():
+    """Sanity of the simulation itself: a producer that does not wait for ACK before pushing
+    must be caught overwriting a slot that its peer has not read yet (for some interleaving)."""
+    caught = 0
+    for seed in range(40):
+        try:
+            drive(3, 2, 1, seed, drop_ack_wait=True)
+        except AssertionError as exc:
+            assert "overwritten before it was read" in str(exc) or "holds" in str(exc)
+            caught += 1
+    assert caught > 0
+
+
+def drive(ws, nbuf, lanes, seed, drop_ack_wait=False):
+    nbytes = 64
+    rounds = 9
+    nparams = rounds * ws - (ws - 1)          # last round has a single producer
+    sim, opses, bufs, gathers = build_world(ws, nbuf, nbytes, seed)
+    consumed = []
+    if drop_ack_wait:
+        for ops in opses:
+            real = ops.wait32_geq
+            # ACK waits are the ones issued on the per-peer push streams (name "r<k>.s<n>")
+            ops.wait32_geq = lambda st, a, v, real=real: None if ".s" in st.name else real(st, a, v)
+
+    for r in range(ws):                        # host program of rank r, as Muon.step issues it
+        ops, pg = opses[r], gathers[r]
+        main = ops.cur
+        lane_streams = [main] + [SimStream(sim, f"r{r}.lane{i}") for i in range(1, lanes)]
+        side = SimStream(sim, f"r{r}.side")
+        upd_done = [None] * nbuf
+        ns_done = [None] * nbuf
+        pending = None                         # (handle, b, producers, round)
+        for i in range(rounds):
+            b = i % nbuf
+            lane = lane_streams[b % lanes]
+            producers = list(range(min(ws, nparams - i * ws)))
+            ops.cur = lane
+            if upd_done[b] is not None:
+                ops.wait_event(lane, upd_done[b])
+                upd_done[b] = None
+            pg.before_slot_write(0, b, lane)
+            slot = bufs[r][b] + r * nbytes
+            if r in producers:
+                def ns(slot=slot, i=i, r=r):
+                    old = sim.mem.get(slot)
+                    assert old is None or old[3], f"own slot rewritten before its update read it: {old}"
+                    sim.mem[slot] = ("slot", r, i, False)
+                lane.push(lambda: True, ns)
+                ns_done[b] = ops.record(lane)
+            else:
+                ns_done[b] = None
+            if pending is not None:
+                h, pb, pprod, pround = pending
+                if ns_done[pb] is not None:
+                    ops.wait_event(side, ns_done[pb])
+                ops.cur = side
+                h.wait()
+
+                def update(pb=pb, pprod=pprod, pround=pround, r=r):
+                    for q in pprod:
+                        a = bufs[r][pb] + q * nbytes
+                        v = sim.mem.get(a)
+                        assert v is not None and v[1] == q and v[2] == pround, \
+                            f"rank {r} round {pround}: slot of {q} holds {v}"
+                        sim.mem[a] = (v[0], v[1], v[2], True)
+                    consumed.append((r, pround))
+                side.push(lambda: True, update)
+                h.done()
+                upd_done[pb] = ops.record(side)
+                ops.cur = lane
+            handle = pg.publish(0, b, slot, nbytes, producers)
+            pending = (handle, b, producers, i)
+        h, pb, pprod, pround = pending
+        if ns_done[pb] is not None:
+            ops.wait_event(side, ns_done[pb])
+        ops.cur = side
+        h.wait()
+
+        def last(pb=pb, pprod=pprod, pround=pround, r=r):
+            for q in pprod:
+                v = sim.mem.get(bufs[r][pb] + q * nbytes)
+                assert v is not None and v[1] == q and v[2] == pround
+            consumed.append((r, pround))
+        side.push(lambda: True, last)
+        h.done()
+
+    sim.run()
+    assert sorted(consumed) == sorted((r, i) for r in range(ws) for i in range(rounds))
