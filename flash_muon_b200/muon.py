@@ -191,6 +191,13 @@ class Muon(torch.optim.Optimizer):
           parameters has been enqueued on ``stream``; work the callback enqueues behind an event
           of that stream (e.g. device-to-host copies) sees the updated parameters.
         """
+        if len(self.param_groups) > 0 and self.param_groups[0]["update_buffer"].is_cuda:
+            # kernels are launched on the device of the buffers, whatever device is current
+            with torch.cuda.device(self.param_groups[0]["update_buffer"].device):
+                return self._step(grad_ready, on_applied)
+        return self._step(grad_ready, on_applied)
+
+    def _step(self, grad_ready, on_applied):
         ws = self.world_size
         overlap = self._overlap_updates and len(self.param_groups) > 0 and \
             self.param_groups[0]["update_buffer"].is_cuda
