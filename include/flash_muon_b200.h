@@ -7,8 +7,10 @@
  *
  * Conventions
  *  - Every function returns an fm_status (0 = ok, negative = error).  Nothing throws.
- *  - All data pointers are DEVICE pointers owned by the caller; nothing is allocated or freed
- *    by the library and nothing synchronises unless stated.
+ *  - All data pointers are DEVICE pointers owned by the caller; no entry point allocates or frees
+ *    memory and nothing synchronises unless stated.  The library's device image carries two
+ *    fixed scratch arrays that exist on every GPU that loads it: ~21 MB for the partial sums of
+ *    the balanced GEMM tail and ~38 MB for fm_newtonschulz_static.
  *  - `stream` is a cudaStream_t passed as void* (0 = the legacy default stream).  All work of a
  *    call is enqueued on that stream of the CURRENT device.
  *  - Leading dimensions and strides are in ELEMENTS.
