@@ -341,12 +341,13 @@ def run_ours(args):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
-    if ws == 1:
-        del params, opt
-        torch.cuda.empty_cache()
+    if rank == 0:
+        # the kernel half of the metric and the roofline of the dominant kernel: rank 0's GPU,
+        # timed alone (the other ranks wait at the barrier below)
         mt, roof = time_syrk(peaks)
         line["matmul_transpose"] = mt
         line["roofline"] = roof
+    if ws == 1:
         threads = os.cpu_count() or 1
         dt, fl = cpu_reference_sample(threads)
         line["cpu_baseline"] = {
