@@ -199,7 +199,7 @@ def time_syrk(peaks, dim=SYRK_DIM, reps=30):
     res = {"shape": [m, k], "ms": t, "tflops_effective": 2 * m * m * k / t / 1e9,
            "tflops_algorithmic": alg / t / 1e9, "tflops_executed": execd / t / 1e9,
            "cublas_ms": tc, "speedup_vs_cublas": tc / t, "reps": reps}
-    # DRAM bytes of one 8192^2 launch from an ncu capture (profiles/gemm_tc2_kernel_syrk_8192_bf16.md)
+    # DRAM bytes of one 8192^2 launch: dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture
     traffic = 692.8e6 + 131.2e6 if m == 8192 else None
     roof = {"kernel": f"gemm_tc2_kernel<bf16> as matmul_transpose {m}x{k}", "bound": "tensor",
             "achieved": alg / t / 1e9, "peak": peaks["bf16"], "unit": "TFLOP/s",

@@ -9,8 +9,8 @@ runs on CPU tensors (the oracle proper) and, unchanged, on CUDA tensors (where i
 "plain PyTorch" comparison for the floating-point kernels).
 
 Pinning: the reference holds no tests, golden vectors or fixtures.  The oracle is pinned against
-outputs of the reference itself run in the build container (``tests/golden/make_golden.py`` imports
-``/root/reference``: ``benchmark.py``'s torch functions unmodified; ``flash_muon/muon.py`` with its
+outputs of the reference itself run on CPU (``tests/golden/make_golden.py`` imports a checkout of
+the reference: ``benchmark.py``'s torch functions unmodified; ``flash_muon/muon.py`` with its
 Triton launch replaced by a CPU matmul, the only part that cannot execute without a GPU; the Triton
 kernel itself under the interpreter in fp32).  ``tests/test_oracle_golden.py`` checks the oracle
 against those committed fixtures.

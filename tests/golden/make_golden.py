@@ -1,7 +1,7 @@
-"""Generates ``tests/golden/reference_outputs.pt`` by running the REFERENCE (nil0x9/flash-muon,
-mounted read-only at /root/reference) on CPU in the build container.
+"""Generates ``tests/golden/reference_outputs.pt`` by running the REFERENCE (a checkout of
+nil0x9/flash-muon) on CPU.
 
-Run from the repo root:  ``python tests/golden/make_golden.py``
+Run from the repo root:  ``python tests/golden/make_golden.py <path-to-flash-muon-checkout>``
 
 The reference cannot execute as shipped without a GPU, so three documented shims are applied to
 the imported modules (none of them touches the arithmetic under test except the first):
@@ -27,7 +27,7 @@ from pathlib import Path
 
 import torch
 
-REF = Path("/root/reference")
+REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("FLASH_MUON_REFERENCE", "reference"))
 OUT = Path(__file__).resolve().parent / "reference_outputs.pt"
 sys.path.insert(0, str(Path(__file__).resolve().parent))
 from inputs import (MUON_HP, muon_case, ns_input, syrk_input, NS_SHAPES, SYRK_CASES)  # noqa: E402
@@ -81,7 +81,7 @@ def run_muon_single(rmuon, steps: int):
 
 _WS2_CHILD = r'''
 import os, sys, torch, torch.distributed as dist
-sys.path.insert(0, "/root/reference"); sys.path.insert(0, sys.argv[1])
+sys.path.insert(0, sys.argv[4]); sys.path.insert(0, sys.argv[1])
 import flash_muon.muon as rmuon
 from inputs import MUON_HP, muon_case
 rank = int(os.environ["RANK"]); ws = int(os.environ["WORLD_SIZE"]); steps = int(sys.argv[2])
@@ -112,7 +112,7 @@ def run_muon_ws(ws: int, steps: int):
         out = str(Path(td) / "res")
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ws}",
                "--master-addr", "127.0.0.1", "--master-port", "29671", str(child),
-               str(Path(__file__).resolve().parent), str(steps), out]
+               str(Path(__file__).resolve().parent), str(steps), out, str(REF)]
         subprocess.run(cmd, check=True, env={**os.environ, "OMP_NUM_THREADS": "2"})
         return [torch.load(out + f".rank{r}") for r in range(ws)]
 
@@ -120,7 +120,7 @@ def run_muon_ws(ws: int, steps: int):
 _INTERP_CHILD = r'''
 import os, sys, torch
 os.environ["TRITON_INTERPRET"] = "1"
-sys.path.insert(0, "/root/reference"); sys.path.insert(0, sys.argv[1])
+sys.path.insert(0, sys.argv[3]); sys.path.insert(0, sys.argv[1])
 from flash_muon.matmul_transpose_triton import mmt_kernel
 from inputs import syrk_input
 x = syrk_input(96, 80, torch.float32)
@@ -136,8 +136,8 @@ def run_triton_interpreter():
         child = Path(td) / "child.py"
         child.write_text(_INTERP_CHILD)
         out = str(Path(td) / "y.pt")
-        subprocess.run([sys.executable, str(child), str(Path(__file__).resolve().parent), out],
-                       check=True)
+        subprocess.run([sys.executable, str(child), str(Path(__file__).resolve().parent), out,
+                        str(REF)], check=True)
         return torch.load(out)
 
 
