@@ -1,0 +1,32 @@
+"""The parts of bench.py that run without a GPU: the reference arm's JSON line and the FLOP /
+byte bookkeeping the roofline figures are computed from."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+import bench  # noqa: E402
+
+
+def test_reference_arm_prints_one_json_line():
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "muon_step_ms" and d["unit"] == "ms"
+    assert d["higher_is_better"] is False and d["value"] > 0
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["e2e"] == {"value": d["value"], "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+
+
+def test_flop_bookkeeping_matches_the_survey_figures():
+    alg, full = bench.full_step_flops()
+    assert abs(alg - 4.7181e14) / 4.7181e14 < 1e-3      # algorithmic FLOPs of one Llama-shaped step
+    assert abs(full - 6.6589e14) / 6.6589e14 < 1e-3     # cuBLAS-equivalent FLOPs
+    a, f = bench.ns_flops(4096, 4096)
+    assert abs(a - 1.3746e12) / 1.3746e12 < 1e-3 and abs(f - 2.0616e12) / 2.0616e12 < 1e-3
+    assert sum(r * c for r, c in bench.LLAMA_LAYER) * bench.N_LAYERS == 6979321856
