@@ -348,6 +348,26 @@ def run_ours(args):
         line["matmul_transpose"] = mt
         line["roofline"] = roof
     if ws == 1:
+        # BASELINE configs[3] for the record (not the headline): GPT-2-medium-shaped set, 24 layers x
+        # {4 x [1024,1024], [4096,1024], [1024,4096]}, same hyper-parameters, one GPU
+        del params, opt, owned, owned_set
+        torch.cuda.empty_cache()
+        gshapes = ([(1024, 1024)] * 4 + [(4096, 1024), (1024, 4096)]) * 24
+        gp = [torch.nn.Parameter((torch.randn(*s, device=dev, generator=g) * 0.02).bfloat16())
+              for s in gshapes]
+        for p in gp:
+            p.grad = (torch.randn(p.shape, device=dev, generator=g) * 1e-3).bfloat16()
+        gopt = fm.Muon(gp, rank=0, world_size=1, **HP)
+        for _ in range(3):
+            gopt.step()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(10):
+            gopt.step()
+        e1.record()
+        torch.cuda.synchronize()
+        line["muon_step_ms_gpt2_medium_shapes"] = e0.elapsed_time(e1) / 10
+        del gp, gopt
         threads = os.cpu_count() or 1
         dt, fl = cpu_reference_sample(threads)
         line["cpu_baseline"] = {
