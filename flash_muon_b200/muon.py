@@ -130,7 +130,8 @@ class Muon(torch.optim.Optimizer):
         if self._peer:
             # load_state_dict() replaces the gather buffers: the exported addresses are stale then
             now = [[b.data_ptr() for b in self._group_buffers(g)[0]] for g in self.param_groups]
-            if now != self._peer.buffer_ptrs:
+            nowp = [[p.data_ptr() for p in g["params"]] for g in self.param_groups]
+            if now != self._peer.buffer_ptrs or nowp != self._peer.param_ptrs:
                 self._peer = None
         if self._peer is None:
             self._peer = False
@@ -142,7 +143,9 @@ class Muon(torch.optim.Optimizer):
                     device = self.param_groups[0]["update_buffer"].device
                     peer = PeerGather(self.rank, self.world_size,
                                       [[b.data_ptr() for b in self._group_buffers(g)[0]]
-                                       for g in self.param_groups], CudaOps(device))
+                                       for g in self.param_groups], CudaOps(device),
+                                      param_addrs=[[p.data_ptr() for p in g["params"]]
+                                                   for g in self.param_groups])
                 except Exception as exc:  # same decision on every rank, taken below
                     ok = 0
                     warnings.warn(f"peer all-gather unavailable ({exc}); using NCCL")
@@ -214,6 +217,13 @@ class Muon(torch.optim.Optimizer):
                 for st in extra:
                     st.wait_stream(main)        # gradients produced on the caller's stream
         peer = self._peer_gather() if (ws > 1 and type(self)._all_gather is Muon._all_gather) else None
+        # Owner-applies-and-pushes-the-parameter exchange (see peer_gather.py): needs the peer
+        # set-up and the event-ordered update stream; FM_MUON_EXCHANGE=updates keeps the
+        # reference's "gather the updates, every rank applies all of them".
+        push_params_ok = peer is not None and overlap and \
+            os.environ.get("FM_MUON_EXCHANGE", "params") != "updates"
+        if peer is not None:
+            peer.begin_step(torch.cuda.current_stream(self.param_groups[0]["update_buffer"].device))
         for gi, group in enumerate(self.param_groups):
             buffers, views = self._group_buffers(group)
             nbuf = len(buffers)
@@ -223,6 +233,10 @@ class Muon(torch.optim.Optimizer):
             prev = 0                   # which buffer the round in flight uses
             ns_done = [None] * nbuf    # per buffer: this rank's slot has been written
             upd_done = [None] * nbuf   # per buffer: its updates have been applied (side stream)
+            # parameters wider than the bf16 updates would cost more link bytes than they save
+            push_params = push_params_ok and all(p.element_size() <= 2 and p.is_contiguous()
+                                                 for p in params)
+            prev_base = 0
 
             def update_prev():
                 if not overlap:
@@ -238,6 +252,22 @@ class Muon(torch.optim.Optimizer):
                 # the tensor-core work of the following rounds instead of between them.
                 if ns_done[prev] is not None:
                     side.wait_event(ns_done[prev])  # this rank's own slot is complete
+                if push_params:
+                    with torch.cuda.stream(side):
+                        mine = prev_base + self.rank
+                        if mine < len(params):  # apply my own update, then hand the result out
+                            self._apply_updates([params[mine]], [views[prev][self.rank]],
+                                                group["lr"], group["weight_decay"])
+                        p_own = params[mine] if mine < len(params) else params[prev_base]
+                        h = peer.publish(gi, prev, p_own.data_ptr(), p_own.numel() * p_own.element_size(),
+                                         list(range(len(params_world))), param_index=mine)
+                        h.wait()            # the peers' parameters of this round have landed here
+                        h.done()
+                        if on_applied is not None:
+                            on_applied(params_world, side)
+                        upd_done[prev] = torch.cuda.Event()
+                        upd_done[prev].record(side)
+                    return
                 with torch.cuda.stream(side):
                     if handle is not None:
                         handle.wait()
@@ -284,17 +314,22 @@ class Muon(torch.optim.Optimizer):
                     # an idle rank contributes whatever its slot holds (muon.py:104-105)
                     if base_i > 0:
                         update_prev()
-                    if peer is not None:
+                    if push_params:
+                        handle = None  # published by update_prev, after the owner's update
+                    elif peer is not None:
                         handle = peer.publish(gi, cur, slot.data_ptr(), slot.numel() * slot.element_size(),
                                               list(range(min(ws, len(params) - base_i))))
                     elif ws > 1:
                         handle = self._all_gather(buffers[cur], slot)
                 params_world = params[base_i: base_i + ws]
                 prev = cur
+                prev_base = base_i
             if params_world is not None:
                 update_prev()
         if overlap:
             main.wait_stream(side)  # the step's effects are ordered on the caller's stream
+            if peer is not None:
+                peer.end_step(main)
             if lanes is not None:
                 for st in lanes[1:]:
                     main.wait_stream(st)

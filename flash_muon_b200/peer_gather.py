@@ -17,6 +17,15 @@ flag rows:
 
 Flag values are per-(producer, buffer) use counters that every rank advances identically, so no
 value is ever reused and a late flag can never be mistaken for an early one.
+
+The same machinery carries a second kind of exchange: instead of gathering every update and
+letting every rank apply it, the OWNER applies decay + update to its copy of the parameter and
+pushes the updated parameter into the replicas of its peers.  All replicas are bit-identical
+before the step and the update is deterministic, so the result is the one the reference computes
+on every rank -- but a rank streams 1/world_size of the parameters through HBM instead of all of
+them.  Since the destination is then live model state rather than a scratch buffer, a producer
+additionally waits for ``STEP[q]``, which consumer ``q`` writes when it enters the same step
+(after whatever it did with the parameters before, e.g. the backward pass).
 Process-to-process addresses come from CUDA IPC handles exchanged once through the existing
 ``torch.distributed`` group.
 
@@ -121,25 +130,35 @@ class PeerGather:
     ``buffer_addrs[g][b]`` is the device address of buffer ``b`` of numel group ``g`` (each
     ``[world_size, numel]``, rows contiguous) on this rank."""
 
-    def __init__(self, rank: int, world_size: int, buffer_addrs: list[list[int]], ops):
+    def __init__(self, rank: int, world_size: int, buffer_addrs: list[list[int]], ops,
+                 param_addrs: list[list[int]] | None = None):
         self.rank, self.ws, self.ops = rank, world_size, ops
         self.ngroups = len(buffer_addrs)
         self.nbuf = max(len(bl) for bl in buffer_addrs)
         self.buffer_ptrs = [list(bl) for bl in buffer_addrs]
-        # [group, buffer, kind, rank] use counters written by peers
-        self._flags_keepalive, flag_addr = ops.alloc_flags(self.ngroups * self.nbuf * 2 * world_size)
+        self.param_ptrs = [list(pl) for pl in (param_addrs or [])]
+        # [group, buffer, kind, rank] use counters written by peers, then STEP[rank]
+        self._step_flags = self.ngroups * self.nbuf * 2 * world_size
+        self._flags_keepalive, flag_addr = ops.alloc_flags(self._step_flags + world_size)
         mine = {"flags": ops.export(flag_addr),
-                "bufs": [[ops.export(a) for a in bl] for bl in buffer_addrs]}
+                "bufs": [[ops.export(a) for a in bl] for bl in buffer_addrs],
+                "params": [[ops.export(a) for a in pl] for pl in self.param_ptrs]}
         everyone = ops.exchange(mine, world_size)
         self._flag_base = [0] * world_size
         self._buf_base = [None] * world_size
+        self._param_base = [None] * world_size
         for r, info in enumerate(everyone):
             if r == rank:
                 self._flag_base[r] = flag_addr
                 self._buf_base[r] = self.buffer_ptrs
+                self._param_base[r] = self.param_ptrs
             else:
                 self._flag_base[r] = ops.import_(info["flags"])
                 self._buf_base[r] = [[ops.import_(h) for h in hl] for hl in info["bufs"]]
+                self._param_base[r] = [[ops.import_(h) for h in hl] for hl in info["params"]]
+        self.step_no = 0
+        self._step_waited: set = set()
+        self._step_events: list = []
         ops.barrier()  # nobody writes a flag before everybody has zeroed and mapped them
         self.streams = {q: ops.new_stream() for q in range(world_size) if q != rank}
         # host-side mirror of the use counters: seq[group][buffer][producer]
@@ -150,6 +169,28 @@ class PeerGather:
     def flag_addr(self, holder: int, gi: int, b: int, kind: int, idx: int) -> int:
         return self._flag_base[holder] + 4 * ((((gi * self.nbuf + b) * 2 + kind) * self.ws) + idx)
 
+    def step_flag_addr(self, holder: int, idx: int) -> int:
+        return self._flag_base[holder] + 4 * (self._step_flags + idx)
+
+    def begin_step(self, stream) -> None:
+        """``stream`` carries whatever this rank did with its parameters before the step: once it
+        gets here, peers may write updated parameters into this rank's replicas."""
+        self.step_no += 1
+        self._step_waited = set()
+        self._step_events = []
+        for q in self.streams:
+            self.ops.write32(stream, self.step_flag_addr(q, self.rank), self.step_no)
+
+    def end_step(self, stream) -> None:
+        """Copies out of this rank's parameters must finish before ``stream`` goes on (the next
+        step rewrites them)."""
+        for ev in self._step_events:
+            self.ops.wait_event(stream, ev)
+        self._step_events = []
+
+    def param_addr(self, holder: int, gi: int, index: int) -> int:
+        return self._param_base[holder][gi][index]
+
     def before_slot_write(self, gi: int, b: int, stream) -> None:
         """``stream`` is about to overwrite this rank's slot of buffer ``b``: earlier copies out
         of it must have finished."""
@@ -157,9 +198,12 @@ class PeerGather:
             self.ops.wait_event(stream, ev)
         self.push_events[gi][b] = []
 
-    def publish(self, gi: int, b: int, slot_addr: int, nbytes: int, producers: list[int]) -> PeerRound:
-        """Called on the stream that produced the slot at ``slot_addr`` (this rank's row of
-        buffer ``b``, ``nbytes`` long)."""
+    def publish(self, gi: int, b: int, slot_addr: int, nbytes: int, producers: list[int],
+                param_index: int | None = None) -> PeerRound:
+        """Called on the stream that produced the ``nbytes`` at ``slot_addr``.  By default they
+        are this rank's row of buffer ``b`` and go to the same row of every peer's buffer ``b``;
+        with ``param_index`` they are this rank's updated parameter ``param_index`` of group
+        ``gi`` and go to the peers' replicas of that parameter."""
         seqs = []
         for r in producers:
             self.seq[gi][b][r] += 1
@@ -169,11 +213,20 @@ class PeerGather:
             ready = self.ops.record(self.ops.current_stream())
             for q, st in self.streams.items():
                 self.ops.wait_event(st, ready)
-                # q has applied the update that read my previous slot in its buffer b
+                # q has consumed what I sent it in the previous use of buffer / flag row b
                 self.ops.wait32_geq(st, self.flag_addr(self.rank, gi, b, ACK, q), s - 1)
-                self.ops.copy(st, self._buf_base[q][gi][b] + self.rank * nbytes, slot_addr, nbytes)
+                if param_index is None:
+                    dst = self._buf_base[q][gi][b] + self.rank * nbytes
+                else:
+                    if q not in self._step_waited:  # q has entered this step
+                        self.ops.wait32_geq(st, self.step_flag_addr(self.rank, q), self.step_no)
+                        self._step_waited.add(q)
+                    dst = self.param_addr(q, gi, param_index)
+                self.ops.copy(st, dst, slot_addr, nbytes)
                 self.ops.write32(st, self.flag_addr(q, gi, b, READY, self.rank), s)
-                self.push_events[gi][b].append(self.ops.record(st))
+                ev = self.ops.record(st)
+                self.push_events[gi][b].append(ev)
+                self._step_events.append(ev)
         return PeerRound(self, gi, b, producers, seqs)
 
     def close(self) -> None:

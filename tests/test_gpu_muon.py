@@ -222,24 +222,27 @@ def test_missing_grad_asserts():
 def _run_ranks(tmp_path, ws, gather):
     child = ROOT / "tests" / "nccl_muon_child.py"
     out = tmp_path / f"res_{gather}_{ws}"
+    port = 29733 + ws + {"peer": 0, "peer_updates": 11, "nccl": 7}[gather]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ws}",
-           "--master-addr", "127.0.0.1", "--master-port", str(29733 + ws + (7 if gather == "nccl" else 0)),
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
            str(child), str(out)]
-    env = {**os.environ, "NCCL_NVLS_ENABLE": "0", "FM_MUON_GATHER": gather}
+    env = {**os.environ, "NCCL_NVLS_ENABLE": "0", "FM_MUON_GATHER": gather.split("_")[0],
+           "FM_MUON_EXCHANGE": "updates" if gather.endswith("_updates") else "params"}
     assert subprocess.run(cmd, env=env, timeout=600).returncode == 0
     return [torch.load(str(out) + f".rank{r}") for r in range(ws)]
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("gather", ["peer", "nccl"])
+@pytest.mark.parametrize("gather", ["peer", "peer_updates", "nccl"])
 def test_ranks_match_single_rank(tmp_path, gather):
-    """All ranks end with identical parameters, bit-equal to world_size 1, with the copy-engine
-    all-gather (DMA pushes ordered by stream-side flags) as with the NCCL one.  Uses every GPU of
-    the box up to 4 (3 gives a partial last round)."""
+    """All ranks end with identical parameters, bit-equal to world_size 1, with the three
+    exchanges: owners push updated parameters by DMA (default), every rank gathers all updates by
+    DMA and applies them, and the NCCL all-gather of updates.  Uses every GPU of the box up to 4
+    (3 gives a partial last round)."""
     ws = min(torch.cuda.device_count(), 4)
     ws = 3 if ws == 4 else ws
     res = _run_ranks(tmp_path, ws, gather)
-    assert all(r["mode"] == gather for r in res)
+    assert all(r["mode"] == gather.split("_")[0] for r in res)
     params, grads = muon_case(2, shapes=MUON_SHAPES + gpt2_medium_shapes(1), seed=9)
     ps, _ = run_product(params, grads, 2, **MUON_HP)
     for i, c in enumerate(ps):

@@ -21,6 +21,8 @@ class Sim:
         self.board = {}
         self.rng = random.Random(seed)
         self.next_addr = 1 << 20
+        self.replica_of = {}     # address of a parameter replica -> rank that holds it
+        self.used = {}           # rank -> last step whose pre-step use of the replicas is over
 
     def alloc(self, nbytes):
         a = self.next_addr
@@ -107,28 +109,39 @@ class SimOps:
         def run():
             payload = self.sim.mem[src]
             old = self.sim.mem.get(dst)
+            if dst in self.sim.replica_of:
+                # live model state: its holder must have entered the step the value belongs to
+                q = self.sim.replica_of[dst]
+                assert self.sim.used.get(q, -1) >= payload[2], \
+                    f"replica of rank {q} overwritten with step {payload[2]} while still in use"
+                self.sim.mem[dst] = payload
+                return
             # the slot being overwritten must have been consumed by its holder
             assert old is None or old[3], f"slot {dst} overwritten before it was read: {old}"
             self.sim.mem[dst] = (payload[0], payload[1], payload[2], False)
         stream.push(lambda: True, run)
 
 
-def build_world(ws, nbuf, numel_bytes, seed):
+def build_world(ws, nbuf, numel_bytes, seed, nparams=0):
     sim = Sim(ws, seed)
     opses = [SimOps(sim, r) for r in range(ws)]
     bufs = [[sim.alloc(ws * numel_bytes) for _ in range(nbuf)] for _ in range(ws)]
+    pars = [[sim.alloc(numel_bytes) for _ in range(nparams)] for _ in range(ws)]
     # PeerGather's constructor is collective: post every rank's exports first, then construct
     gathers = []
     # phase 1: flags + exports per rank (mimic the constructor's first half)
     posted = {}
     for r, ops in enumerate(opses):
-        keep, fa = ops.alloc_flags(1 * nbuf * 2 * ws)
-        posted[r] = {"flags": ops.export(fa), "bufs": [[ops.export(a) for a in bufs[r]]]}
+        keep, fa = ops.alloc_flags(1 * nbuf * 2 * ws + ws)
+        posted[r] = {"flags": ops.export(fa), "bufs": [[ops.export(a) for a in bufs[r]]],
+                     "params": [[ops.export(a) for a in pars[r]]]}
         ops._prealloc = (keep, fa)
     for r, ops in enumerate(opses):
         ops.alloc_flags = lambda n, o=ops: o._prealloc
         ops.exchange = lambda obj, w, p=posted: [p[i] for i in range(w)]
-        gathers.append(PeerGather(r, ws, [bufs[r]], ops))
+        gathers.append(PeerGather(r, ws, [bufs[r]], ops, param_addrs=[pars[r]]))
+    if nparams:
+        return sim, opses, bufs, gathers, pars
     return sim, opses, bufs, gathers
 
 
@@ -227,3 +240,101 @@ def drive(ws, nbuf, lanes, seed, drop_ack_wait=False):
 
     sim.run()
     assert sorted(consumed) == sorted((r, i) for r in range(ws) for i in range(rounds))
+
+
+@pytest.mark.parametrize("ws,nbuf,lanes", [(2, 2, 1), (3, 4, 2), (4, 8, 4)])
+@pytest.mark.parametrize("seed", range(10))
+def test_parameter_push_exchange_over_two_steps(ws, nbuf, lanes, seed):
+    drive_params(ws, nbuf, lanes, seed)
+
+
+def test_simulation_catches_pushes_that_do_not_wait_for_the_step_flag():
+    caught = 0
+    for seed in range(40):
+        try:
+            drive_params(3, 4, 2, seed, drop_step_wait=True)
+        except AssertionError as exc:
+            assert "while still in use" in str(exc) or "holds" in str(exc)
+            caught += 1
+    assert caught > 0
+
+
+def drive_params(ws, nbuf, lanes, seed, drop_step_wait=False):
+    """The owner applies the update and pushes the parameter into its peers' replicas.  Between
+    two steps every rank 'uses' its replicas (as a forward/backward pass would): no replica may
+    change before its rank has entered the next step, every replica must carry the owner's value
+    of the step when the step ends."""
+    nbytes = 64
+    rounds = 5
+    nparams = rounds * ws - 1                      # last round: one rank idle
+    sim, opses, bufs, gathers, pars = build_world(ws, nbuf, nbytes, seed, nparams=nparams)
+    for r in range(ws):
+        for i in range(nparams):
+            sim.mem[pars[r][i]] = ("param", i % ws, -1, True)    # identical replicas, step -1
+            sim.replica_of[pars[r][i]] = r
+
+    for r in range(ws):
+        ops, pg = opses[r], gathers[r]
+        main = ops.cur
+        lane_streams = [main] + [SimStream(sim, f"r{r}.lane{i}") for i in range(1, lanes)]
+        side = SimStream(sim, f"r{r}.side")
+        for step in range(2):
+            # the training loop reads the replicas before the step (all must be of step-1)
+            def use(r=r, step=step):
+                for i in range(nparams):
+                    v = sim.mem[pars[r][i]]
+                    assert v[2] == step - 1, f"rank {r} before step {step}: param {i} holds {v}"
+                sim.used[r] = step
+            main.push(lambda: True, use)
+            ops.cur = main
+            pg.begin_step(main)
+            if drop_step_wait:
+                pg._step_waited = set(range(ws))   # pretend every peer was already waited for
+            for st in lane_streams[1:]:
+                ops.wait_event(st, ops.record(main))
+            upd_done = [None] * nbuf
+            pending = None
+            for i in range(rounds):
+                b = i % nbuf
+                lane = lane_streams[b % lanes]
+                base = i * ws
+                world = list(range(base, min(base + ws, nparams)))
+                if upd_done[b] is not None:
+                    ops.wait_event(lane, upd_done[b])
+                    upd_done[b] = None
+                mine = base + r
+                ns_done = None
+                if mine < nparams:
+                    lane.push(lambda: True, lambda: None)          # momentum + Newton-Schulz
+                    ns_done = ops.record(lane)
+                if pending is not None:
+                    _flush(sim, ops, pg, side, pars, r, nbytes, pending, upd_done, step)
+                pending = (b, base, world, mine, ns_done)
+            _flush(sim, ops, pg, side, pars, r, nbytes, pending, upd_done, step)
+            # join: side stream and pushes, then the step is over on main
+            ops.wait_event(main, ops.record(side))
+            pg.end_step(main)
+
+            def check_end(r=r, step=step):
+                for i in range(nparams):
+                    v = sim.mem[pars[r][i]]
+                    assert v[1] == i % ws and v[2] == step, f"rank {r} after step {step}: param {i} holds {v}"
+            main.push(lambda: True, check_end)
+    sim.run()
+
+
+def _flush(sim, ops, pg, side, pars, r, nbytes, pending, upd_done, step):
+    b, base, world, mine, ns_done = pending
+    if ns_done is not None:
+        ops.wait_event(side, ns_done)
+    ops.cur = side
+    nparams = len(pars[r])
+    if mine < nparams:
+        def own_update(a=pars[r][mine], r=r, step=step):
+            sim.mem[a] = ("param", r, step, True)
+        side.push(lambda: True, own_update)
+    src = pars[r][mine] if mine < nparams else pars[r][base]
+    h = pg.publish(0, b, src, nbytes, list(range(len(world))), param_index=mine)
+    h.wait()
+    h.done()
+    upd_done[b] = ops.record(side)
