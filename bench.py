@@ -320,9 +320,11 @@ def run_ours(args):
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / k2)
 
     # launches of this library's kernels per step on this rank: per owned matrix 1 momentum,
-    # 2 normalisation, 3 GEMMs per Newton-Schulz step; per round one multi-tensor update
+    # 2 normalisation, 3 GEMMs per Newton-Schulz step; per round one multi-tensor update, or one
+    # update per owned matrix when owners push updated parameters to their peers
     rounds = sum((len(grp["params"]) + ws - 1) // ws for grp in opt.param_groups)
-    launches_per_step = len(owned) * (1 + 2 + 3 * HP["ns_steps"]) + rounds
+    pushes_params = bool(getattr(opt, "_peer", None)) and os.environ.get("FM_MUON_EXCHANGE", "params") != "updates"
+    launches_per_step = len(owned) * (1 + 2 + 3 * HP["ns_steps"]) + (len(owned) if pushes_params else rounds)
     alg, full = full_step_flops()
     alg, full = alg * args.layers / N_LAYERS, full * args.layers / N_LAYERS
 
@@ -333,6 +335,8 @@ def run_ours(args):
         "config": {"workload": "Muon.step on Llama-3-8B-shaped matrices (BASELINE configs[4])",
                    "layers": args.layers, "matrices": len(shapes), "elements": sum(a * b for a, b in shapes),
                    "ns_steps": HP["ns_steps"], "parallelism": f"dp{ws} round-robin ownership",
+                   "exchange": ("none" if ws == 1 else "owners push updated parameters (DMA)" if pushes_params
+                                else "all-gather of updates"),
                    "l2": "working set (42+ GB) far larger than L2; no flush needed"},
         "step_tflops_algorithmic": alg / ms / 1e9, "step_tflops_cublas_equivalent": full / ms / 1e9,
         "step_frac_of_sustained_peak": alg / ms / 1e9 / ws / peaks["bf16_sustained"],
