@@ -23,6 +23,7 @@
 #include "gemm_common.cuh"
 #include "gemm_tc.cuh"
 #include "ptx.cuh"
+#include "tile_schedule.cuh"
 
 namespace fm {
 
@@ -42,51 +43,6 @@ struct Cfg {
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kSmemBytes = kStages * kStageBytes + kNumBars * 8 + 16 + 1024;
 };
-
-struct Tile {
-  int m0;     // first output row
-  int n0;     // first output column
-  int ncols;  // 128 or 256 (UMMA N)
-  int bi;     // 128-row block index (for the diagonal test)
-};
-
-// Tiles before column super-tile j of the triangular schedule (R = BN / 128).
-template <int R>
-__host__ __device__ __forceinline__ long long tri_before(long long j) {
-  return R == 1 ? j * (j + 1) / 2 : j * (j + 1);
-}
-
-template <int BN>
-__device__ __forceinline__ Tile decode_tile(const GemmParams& p, int t) {
-  constexpr int R = BN / 128;
-  Tile o;
-  int nblk0;
-  if (!p.sym) {
-    const int tn = t / p.tiles_m;
-    const int tm = t - tn * p.tiles_m;
-    o.m0 = tm * BM;
-    o.bi = tm;
-    nblk0 = tn * R;
-    o.ncols = BN;
-  } else {
-    // Column super-tile j owns row blocks i in [0, min(R*j + R, tiles_m)); only the last column
-    // can be clipped, so tri_before() is exact for every column start.
-    int j = R == 1 ? (int)((sqrtf(8.f * (float)t + 1.f) - 1.f) * 0.5f)
-                   : (int)((sqrtf(4.f * (float)t + 1.f) - 1.f) * 0.5f);
-    while (tri_before<R>(j + 1) <= t) ++j;
-    while (tri_before<R>(j) > t) --j;
-    const int i = t - (int)tri_before<R>(j);
-    o.m0 = i * BM;
-    o.bi = i;
-    const int sub = (i > R * j) ? (i - R * j) : 0;  // leading 128-column blocks below the diagonal
-    nblk0 = R * j + sub;
-    o.ncols = BN - sub * 128;
-  }
-  o.n0 = nblk0 * 128;
-  const int left = p.N - o.n0;  // > 0 by construction
-  if (left <= 128 && o.ncols > 128) o.ncols = 128;
-  return o;
-}
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -248,17 +204,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   if (threadIdx.x == 0) FM_TRACE_MARK(p, 7);
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 0x47450000u | (unsigned)blockIdx.x);
-}
-
-template <int BN>
-int count_tiles(int M, int N, int sym) {
-  constexpr int R = BN / 128;
-  const int tiles_m = (M + 127) / 128;
-  const int tiles_n = (N + BN - 1) / BN;
-  if (!sym) return tiles_m * tiles_n;
-  long long n = 0;
-  for (int j = 0; j < tiles_n; ++j) n += (R * j + R < tiles_m) ? (R * j + R) : tiles_m;
-  return (int)n;
 }
 
 template <typename T, int BN>

@@ -20,6 +20,7 @@
 #include "gemm_common.cuh"
 #include "gemm_tc.cuh"
 #include "ptx.cuh"
+#include "tile_schedule.cuh"
 
 namespace fm {
 namespace {
@@ -33,81 +34,6 @@ constexpr int kStageBytes = 2 * kSlabBytes;   // this CTA's A slab + B slab
 constexpr int kTmemCols = 512;                // two accumulators of 256 fp32 columns
 constexpr int kNumBars = 2 * kMaxStages + 4;
 constexpr int smem_bytes(int stages) { return stages * kStageBytes + kNumBars * 8 + 16 + 1024; }
-
-struct Tile2 {
-  int m0, n0;  // first row / column of the 256 x 256 tile
-};
-
-// Work of one CTA pair.  The first `sk_dp_tiles` tiles of the list are dealt round-robin, one
-// whole tile at a time.  The rest (between one and two waves' worth; empty unless the host
-// decides that balancing pays, see plan_schedule) is cut by K blocks into equal contiguous shares, so
-// that every pair finishes at the same time instead of most of them idling through a last
-// partial wave.  A pair walks its share from the END: first the range that begins a tile it
-// cannot finish -- that partial accumulator is deposited in fp32 scratch right away -- then
-// whole tiles, last the range that finishes a tile begun by earlier pairs.  There the deposits
-// of those pairs (made at the start of their shares, so long since complete) are added in a
-// fixed order to the accumulator and the tile's epilogue runs as usual.  The result does not
-// depend on timing; the wait for the deposits is a formality with the usual cycle limit.
-struct WorkItem {
-  int tile;      // index into the tile list
-  int kb0, kb1;  // K-block range
-  int sk_tile;   // index of the tile inside the balanced region
-  int deposit;   // 1: range stops short of the tile's last K block -> deposit, no epilogue
-  int gather;    // 1: range finishes a tile whose first K blocks were done by earlier pairs
-};
-
-struct WorkIter {
-  int dp_next, dp_step, dp_end;
-  long long lo, hi;
-  __device__ WorkIter(const GemmParams& p, int pair, int npairs) {
-    dp_next = pair;
-    dp_step = npairs;
-    dp_end = p.sk_dp_tiles;
-    lo = (long long)pair * p.sk_per;
-    hi = lo + p.sk_per;
-    if (hi > p.sk_total) hi = p.sk_total;
-    if (lo > hi) lo = hi;
-  }
-  __device__ bool next(const GemmParams& p, WorkItem& w) {
-    if (dp_next < dp_end) {
-      w.tile = dp_next; w.kb0 = 0; w.kb1 = p.num_kb; w.sk_tile = 0; w.deposit = 0; w.gather = 0;
-      dp_next += dp_step;
-      return true;
-    }
-    if (hi > lo) {
-      const int rel = (int)((hi - 1) / p.num_kb);
-      const long long t_begin = (long long)rel * p.num_kb;
-      const long long seg_lo = lo > t_begin ? lo : t_begin;
-      w.tile = p.sk_dp_tiles + rel;
-      w.sk_tile = rel;
-      w.kb0 = (int)(seg_lo - t_begin);
-      w.kb1 = (int)(hi - t_begin);
-      w.deposit = (w.kb1 != p.num_kb) ? 1 : 0;
-      w.gather = (w.kb0 != 0 && !w.deposit) ? 1 : 0;
-      hi = seg_lo;
-      return true;
-    }
-    return false;
-  }
-};
-
-__device__ __forceinline__ Tile2 decode_tile2(const GemmParams& p, int t) {
-  Tile2 o;
-  if (!p.sym) {
-    const int tn = t / p.tiles_m;
-    const int tm = t - tn * p.tiles_m;
-    o.m0 = tm * 256;
-    o.n0 = tn * 256;
-  } else {
-    int j = (int)((sqrtf(8.f * (float)t + 1.f) - 1.f) * 0.5f);
-    while ((long long)(j + 1) * (j + 2) / 2 <= t) ++j;
-    while ((long long)j * (j + 1) / 2 > t) --j;
-    const int i = t - j * (j + 1) / 2;
-    o.m0 = i * 256;
-    o.n0 = j * 256;
-  }
-  return o;
-}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -447,27 +373,18 @@ int plan_schedule(GemmParams& p, int max_pairs, cudaStream_t stream, SkScratch**
   p.sk_cnt = nullptr;
   *used = nullptr;
   if (!sk_enabled() || max_pairs > kSkMaxPairs) return P;
-  // Worth it only when the idle time of the last partial wave exceeds what the partial sums
-  // cost.  Measured on B200 (same process, alternating): 8192^2 and 6144^2 products gain 7-10 %;
-  // lists of one or two waves, or tiles with K <= 4096, lose 2-15 %.  Model: a K block of a
-  // 256 x 256 tile takes ~0.41 us, depositing and re-reading partial accumulators ~12 us per
-  // pair, so balance when the K blocks saved, num_kb * (P - R) / P, are worth more than ~24 us.
-  if (T <= max_pairs) return P;
-  const int R = T % max_pairs;
-  if (R == 0) return P;
-  if ((long long)p.num_kb * (max_pairs - R) < 58LL * max_pairs) return P;
-  const int pairs = max_pairs;
-  const int dp_tiles = (T / max_pairs - 1) * max_pairs;  // leave between one and two waves to balance
+  int dp_tiles = 0, per = 0;
+  long long total = 0;
+  if (!plan_balance(T, p.num_kb, max_pairs, &dp_tiles, &per, &total)) return P;
   SkScratch* sc = sk_acquire(stream);
   if (sc == nullptr) return P;
-  const long long total = (long long)(T - dp_tiles) * p.num_kb;
   p.sk_dp_tiles = dp_tiles;
   p.sk_total = total;
-  p.sk_per = (int)((total + pairs - 1) / pairs);
+  p.sk_per = per;
   p.sk_ws = sc->ws;
   p.sk_cnt = sc->cnt;
   *used = sc;
-  return pairs;
+  return max_pairs;
 }
 
 template <typename T>
@@ -529,8 +446,7 @@ int max_pairs_for() {
 }  // namespace
 
 int gemm_tc2_tiles(int64_t M, int64_t N, int sym) {
-  const int64_t tm = (M + 255) / 256, tn = (N + 255) / 256;
-  return (int)(sym ? tn * (tn + 1) / 2 : tm * tn);
+  return count_tiles2(M, N, sym);
 }
 
 int gemm_tc2_max_pairs(int dtype) {
