@@ -23,6 +23,17 @@ _DTYPES = {torch.bfloat16: FM_BF16, torch.float16: FM_F16, torch.float32: FM_F32
 c_void_p, c_int, c_int64, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
 c_float, c_double = ctypes.c_float, ctypes.c_double
 
+class MuonGroup(ctypes.Structure):
+    """``fm_muon_group`` of include/flash_muon_b200.h."""
+    _fields_ = [("params", ctypes.POINTER(c_void_p)), ("grads", ctypes.POINTER(c_void_p)),
+                ("momentum", ctypes.POINTER(c_void_p)), ("rows", ctypes.POINTER(c_int64)),
+                ("cols", ctypes.POINTER(c_int64)), ("alphas", ctypes.POINTER(c_double)),
+                ("count", ctypes.c_int32), ("p_dtype", ctypes.c_int32), ("g_dtype", ctypes.c_int32),
+                ("nesterov", ctypes.c_int32), ("ns_steps", ctypes.c_int32), ("lanes", ctypes.c_int32),
+                ("momentum_coef", c_double), ("decay", c_double),
+                ("slots", ctypes.POINTER(c_void_p))]
+
+
 # name -> (restype, argtypes); mirrors include/flash_muon_b200.h one to one
 SIGNATURES = {
     "fm_version": (c_int, []),
@@ -53,6 +64,8 @@ SIGNATURES = {
     "fm_update_multi": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                 ctypes.POINTER(c_int64), ctypes.POINTER(c_double), c_int, c_int,
                                 c_double, c_void_p]),
+    "fm_muon_step": (c_int, [ctypes.POINTER(MuonGroup), c_int, ctypes.POINTER(c_void_p),
+                             ctypes.c_size_t, c_void_p]),
 }
 
 

@@ -30,10 +30,12 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-from ._lib import check, current_stream_ptr, dtype_code, lib
+from ._lib import MuonGroup, check, current_stream_ptr, dtype_code, lib
 from .ops import fast_newtonschulz, newtonschulz_workspace_bytes
 
 __all__ = ["Muon"]
+
+_NATIVE_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 
 
 class Muon(torch.optim.Optimizer):
@@ -200,8 +202,84 @@ class Muon(torch.optim.Optimizer):
                 return self._step(grad_ready, on_applied)
         return self._step(grad_ready, on_applied)
 
+    def _native_step(self) -> bool:
+        """The whole step as one C call (``fm_muon_step``) when there is nothing for Python to do
+        between rounds: one rank, no hooks, the stock device operations.  Returns False (having
+        done nothing) when the round loop below has to run instead.  Same kernels in the same
+        order per matrix as the loop, so the parameters come out bit-identical; what goes away
+        is the per-round stream and event bookkeeping on the host."""
+        cls = type(self)
+        if not (self._overlap_updates and self._two_lanes
+                and cls._momentum is Muon._momentum and cls._orthogonalize is Muon._orthogonalize
+                and cls._apply_updates is Muon._apply_updates
+                and os.environ.get("FM_MUON_NATIVE", "1") != "0"):
+            return False
+        device = self.param_groups[0]["update_buffer"].device
+        plan = []
+        need = 0
+        for group in self.param_groups:
+            params = group["params"]
+            if not params:
+                continue
+            p0 = params[0]
+            if len(self._group_buffers(group)[0]) < 2 * group.get("lanes", 2):
+                return False
+            for p in params:
+                g = p.grad
+                assert g is not None
+                if (g.ndim not in (2, 4) or p.dtype != p0.dtype or g.dtype != p0.grad.dtype
+                        or not g.is_contiguous() or not p.is_contiguous() or g.device != device
+                        or p.dtype not in _NATIVE_DTYPES or g.dtype not in _NATIVE_DTYPES):
+                    return False
+            plan.append(group)
+        groups = (MuonGroup * max(len(plan), 1))()
+        keep = []  # ctypes arrays must outlive the call
+        for gs, group in zip(groups, plan):
+            params = group["params"]
+            n = len(params)
+            lr, nes = group["lr"], group["nesterov"]
+            bufs = []
+            for p in params:
+                state = self.state[p]
+                if "momentum_buffer" not in state:
+                    state["momentum_buffer"] = torch.zeros_like(p.grad)
+                bufs.append(state["momentum_buffer"].data_ptr())
+            rows = [p.grad.size(0) for p in params]
+            cols = [p.grad.numel() // max(r, 1) for p, r in zip(params, rows)]
+            need = max([need] + [newtonschulz_workspace_bytes(r, c) for r, c in set(zip(rows, cols))])
+            lanes = group.get("lanes", 2)
+            slots, _ = self._group_buffers(group)
+            arrays = (
+                (ctypes.c_void_p * n)(*[p.data_ptr() for p in params]),
+                (ctypes.c_void_p * n)(*[p.grad.data_ptr() for p in params]),
+                (ctypes.c_void_p * n)(*bufs),
+                (ctypes.c_int64 * n)(*rows),
+                (ctypes.c_int64 * n)(*cols),
+                (ctypes.c_double * n)(*[-lr * max(1, p.size(-2) / p.size(-1)) ** 0.5 for p in params]),
+                (ctypes.c_void_p * (2 * lanes))(*[b.data_ptr() for b in slots[:2 * lanes]]),
+            )
+            keep.append(arrays)
+            (gs.params, gs.grads, gs.momentum, gs.rows, gs.cols, gs.alphas, gs.slots) = arrays
+            gs.count, gs.lanes = n, lanes
+            gs.p_dtype, gs.g_dtype = dtype_code(params[0].dtype), dtype_code(params[0].grad.dtype)
+            gs.nesterov, gs.ns_steps = (1 if nes else 0), int(group["ns_steps"])
+            gs.momentum_coef = float(group["momentum"])
+            gs.decay = 1 - lr * group["weight_decay"]
+        nlanes = max([g.get("lanes", 2) for g in plan], default=1)
+        for lane in range(nlanes):
+            ws = self._workspaces.get(lane)
+            if ws is None or ws.numel() < need or ws.device != device:
+                self._workspaces[lane] = torch.empty(need, dtype=torch.uint8, device=device)
+        wptrs = (ctypes.c_void_p * nlanes)(*[self._workspaces[i].data_ptr() for i in range(nlanes)])
+        wbytes = min(self._workspaces[i].numel() for i in range(nlanes))
+        check(lib.fm_muon_step(groups, len(plan), wptrs, wbytes, current_stream_ptr(device)))
+        return True
+
     def _step(self, grad_ready, on_applied):
         ws = self.world_size
+        if (ws == 1 and grad_ready is None and on_applied is None and len(self.param_groups) > 0
+                and self.param_groups[0]["update_buffer"].is_cuda and self._native_step()):
+            return
         overlap = self._overlap_updates and len(self.param_groups) > 0 and \
             self.param_groups[0]["update_buffer"].is_cuda
         lanes = None

@@ -156,6 +156,51 @@ int fm_update_multi(void* const* params, const void* const* updates, const int64
                     const double* alphas, int count, int p_dtype, double decay, void* stream);
 
 /*
+ * One numel group of a Muon step on one GPU (all arrays are HOST arrays of `count` entries).
+ * Matrix i is params[i] (dtype p_dtype) with gradient grads[i] and momentum buffer momentum[i]
+ * (both g_dtype), all contiguous, seen as rows[i] x cols[i] (conv filters: size(0) x the rest,
+ * flash_muon/muon.py:101-102).  alphas[i] = -lr * sqrt(max(1, size(-2) / size(-1))) of the
+ * ORIGINAL shape (muon.py:89), decay = 1 - lr * weight_decay (muon.py:87).  slots holds
+ * 2 * lanes device buffers of rows*cols bf16 each: the update of round i is written to slot
+ * i mod (2 * lanes), the role the reference's update_buffer plays (muon.py:69, :103).
+ */
+typedef struct {
+  void* const* params;
+  void* const* grads;
+  void* const* momentum;
+  const int64_t* rows;
+  const int64_t* cols;
+  const double* alphas;
+  int32_t count;
+  int32_t p_dtype;
+  int32_t g_dtype;
+  int32_t nesterov;
+  int32_t ns_steps;
+  int32_t lanes;        /* 1..4 streams the rounds of this group rotate over */
+  double momentum_coef; /* mu of muon.py:99-100 */
+  double decay;
+  void* const* slots;
+} fm_muon_group;
+
+/*
+ * A whole Muon step with world_size == 1 in one call: for every matrix of every group, in order,
+ * momentum + Nesterov, Newton-Schulz into an update slot, decay + update.  Replaces the Python
+ * round loop of Muon.step, flash_muon/muon.py:77-110, for the case without an exchange between
+ * ranks; the device work per matrix is that of fm_momentum, fm_newtonschulz and fm_update_multi
+ * in the same order, so the parameters come out bit-identical to driving those from a host loop.
+ * Rounds rotate over lanes: lane 0 is `stream`, the others and the stream of the decay + update
+ * kernels belong to the library (created on the first call per device, as are the events that
+ * order them); all of them wait for `stream` at entry and `stream` waits for all of them before
+ * the call returns, so to the caller the step is ordinary work on `stream`.
+ * workspaces: HOST array of one device buffer of workspace_bytes per lane (as many as the
+ * largest `lanes` of the groups), each at least fm_ns_workspace_bytes of the largest matrix.
+ * One step at a time per device.  gradients are overwritten when nesterov != 0, as by the
+ * reference (muon.py:100).
+ */
+int fm_muon_step(const fm_muon_group* groups, int ngroups, void* const* workspaces,
+                 size_t workspace_bytes, void* stream);
+
+/*
  * Peer-memory plumbing of the copy-engine all-gather that stands in for
  * dist.all_gather_into_tensor (flash_muon/muon.py:108) inside one NVLink-connected box.  Each rank
  * copies its finished slot into every peer's gather buffer with DMA engines and orders the

@@ -71,6 +71,22 @@ def test_host_only_calls():
     assert lib.fm_copy_async(None, None, 16, None) == -1
 
 
+def test_whole_step_call_validates_before_any_cuda_call():
+    """fm_muon_step rejects malformed groups on the host; the struct layout is the header's."""
+    import ctypes
+    from flash_muon_b200 import _lib
+    assert ctypes.sizeof(_lib.MuonGroup) == 6 * 8 + 6 * 4 + 2 * 8 + 8
+    g = _lib.MuonGroup()
+    g.count, g.lanes = 1, 2
+    assert _lib.lib.fm_muon_step(g, 1, None, 0, None) == -1          # null workspace list
+    w = (ctypes.c_void_p * 1)(0)
+    assert _lib.lib.fm_muon_step(g, 1, w, 0, None) == -1             # null arrays in the group
+    assert b"null array" in _lib.lib.fm_last_error()
+    assert _lib.lib.fm_muon_step(None, 0, None, 0, None) == 0        # nothing to do
+    g.count = -1
+    assert _lib.lib.fm_muon_step(g, 1, w, 0, None) == -1
+
+
 def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     """No fallback: pointing the loader at a missing file raises ImportError."""
     import importlib

@@ -96,6 +96,31 @@ def test_config3_gpt2_medium_shapes_one_step():
     _lib.device_status()
 
 
+@pytest.mark.parametrize("nesterov", [True, False])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+def test_whole_step_call_matches_the_round_loop(nesterov, dt, monkeypatch):
+    """``fm_muon_step`` (one C call per step, the default at world_size 1) against the Python round
+    loop over fm_momentum / fm_newtonschulz / fm_update_multi: parameters, momentum buffers and
+    overwritten gradients bit for bit, over several steps, wide / tall / narrow / conv shapes."""
+    steps = 3
+    hp = dict(MUON_HP, nesterov=nesterov)
+    shapes = list(MUON_SHAPES) + [(1024, 256), (256, 1024), (512, 512)] * 3 + [(64, 8, 3, 3)]
+    params, grads = muon_case(steps, shapes=shapes, dtype=dt, seed=11)
+    monkeypatch.setenv("FM_MUON_NATIVE", "0")
+    loop_ps, loop_opt = run_product(params, grads, steps, **hp)
+    monkeypatch.setenv("FM_MUON_NATIVE", "1")
+    called = []
+    real = fm.muon.lib.fm_muon_step
+    monkeypatch.setattr(fm.muon.lib, "fm_muon_step", lambda *a: called.append(1) or real(*a))
+    ps, opt = run_product(params, grads, steps, **hp)
+    assert len(called) == steps                       # the C call really carried every step
+    for a, b in zip(ps, loop_ps):
+        assert torch.equal(a, b)
+        assert torch.equal(a.grad, b.grad)
+        assert torch.equal(opt.state[a]["momentum_buffer"], loop_opt.state[b]["momentum_buffer"])
+    _lib.device_status()
+
+
 def test_state_dict_layout_and_side_effects():
     params, grads = muon_case(1)
     ps, opt = run_product(params, grads, 1, **MUON_HP)

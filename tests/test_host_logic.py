@@ -83,3 +83,86 @@ def test_muon_step_control_flow_over_gloo(ws, tmp_path, golden):
             assert torch.equal(p, ref)
         if ws > 1:
             assert res["owned"] == golden[f"muon_step/ws{ws}/owned"][r]
+
+
+def test_whole_step_call_receives_the_reference_step_arguments(monkeypatch):
+    """What ``Muon.step`` hands to ``fm_muon_step`` at world_size 1: every parameter once, grouped
+    by numel in the optimizer's order, with the 2-D view of conv filters (flash_muon/muon.py:101-
+    102), the update scale of the ORIGINAL shape (muon.py:89), the decay of muon.py:87 and the
+    momentum buffers created on first use (muon.py:96-97).  The C call itself is replaced by a
+    recorder, so this runs without a GPU."""
+    import ctypes
+    from flash_muon_b200 import muon as M
+
+    class CpuMuon(fm.Muon):
+        _buffer_device = "cpu"
+
+    torch.manual_seed(0)
+    shapes = [(64, 32), (32, 64), (16, 8, 3, 3), (48, 48), (64, 32)]
+    params = [torch.nn.Parameter(torch.randn(*s).bfloat16()) for s in shapes]
+    for p in params:
+        p.grad = torch.randn(*p.shape).bfloat16()
+    opt = CpuMuon(params, lr=0.05, weight_decay=0.1, momentum=0.9, nesterov=False, ns_steps=3,
+                  rank=0, world_size=1)
+    seen = {}
+
+    def recorder(groups, ngroups, wptrs, wbytes, stream):
+        seen["ngroups"] = ngroups
+        seen["groups"] = []
+        for i in range(ngroups):
+            g = groups[i]
+            n = g.count
+            seen["groups"].append(dict(
+                params=[g.params[j] for j in range(n)], grads=[g.grads[j] for j in range(n)],
+                momentum=[g.momentum[j] for j in range(n)], rows=[g.rows[j] for j in range(n)],
+                cols=[g.cols[j] for j in range(n)], alphas=[g.alphas[j] for j in range(n)],
+                slots=[g.slots[j] for j in range(2 * g.lanes)], lanes=g.lanes, p_dtype=g.p_dtype,
+                g_dtype=g.g_dtype, nesterov=g.nesterov, ns_steps=g.ns_steps, mu=g.momentum_coef,
+                decay=g.decay))
+        seen["wbytes"] = wbytes
+        seen["lanes_with_workspace"] = [wptrs[i] for i in range(max(g["lanes"] for g in seen["groups"]))]
+        return 0
+
+    monkeypatch.setattr(M.lib, "fm_muon_step", recorder)
+    monkeypatch.setattr(M, "current_stream_ptr", lambda device: None)
+    assert opt._native_step() is True
+    assert seen["ngroups"] == len(opt.param_groups) == 3
+    flat = []
+    for got, group in zip(seen["groups"], opt.param_groups):
+        ps = group["params"]
+        flat += ps
+        assert got["params"] == [p.data_ptr() for p in ps]
+        assert got["grads"] == [p.grad.data_ptr() for p in ps]
+        assert got["momentum"] == [opt.state[p]["momentum_buffer"].data_ptr() for p in ps]
+        assert all(torch.count_nonzero(opt.state[p]["momentum_buffer"]) == 0 for p in ps)
+        assert got["rows"] == [p.shape[0] for p in ps]
+        assert got["cols"] == [p.numel() // p.shape[0] for p in ps]
+        assert got["alphas"] == [-0.05 * max(1, p.size(-2) / p.size(-1)) ** 0.5 for p in ps]
+        bufs, _ = opt._group_buffers(group)
+        assert got["slots"] == [b.data_ptr() for b in bufs[:2 * got["lanes"]]]
+        assert (got["p_dtype"], got["g_dtype"], got["nesterov"], got["ns_steps"]) == (0, 0, 0, 3)
+        assert got["mu"] == 0.9 and got["decay"] == 1 - 0.05 * 0.1
+    assert sorted(id(p) for p in flat) == sorted(id(p) for p in params)
+    # conv filter: 16 x 72 view, scale of the kernel dims (3 / 3 -> 1)
+    conv = [g for g in seen["groups"] if g["rows"] == [16]][0]
+    assert conv["cols"] == [72] and conv["alphas"] == [-0.05]
+    need = max(M.newtonschulz_workspace_bytes(r, c) for g in seen["groups"] for r, c in zip(g["rows"], g["cols"]))
+    assert seen["wbytes"] >= need and all(seen["lanes_with_workspace"])
+
+    # anything the C call cannot express goes back to the round loop: strided gradients,
+    # overridden device operations, the environment switch
+    monkeypatch.setenv("FM_MUON_NATIVE", "0")
+    assert opt._native_step() is False
+    monkeypatch.delenv("FM_MUON_NATIVE")
+    params[3].grad = torch.randn(48, 48).bfloat16().t()       # not contiguous
+    assert opt._native_step() is False
+    params[3].grad = torch.randn(48, 48).bfloat16()
+    assert opt._native_step() is True
+
+    class Hooked(CpuMuon):
+        def _momentum(self, g, buf, momentum, nesterov):
+            return g
+    assert Hooked(params, rank=0, world_size=1)._native_step() is False
+    params[1].grad = None
+    with pytest.raises(AssertionError):
+        opt._native_step()
