@@ -17,7 +17,15 @@ What differs is how the device work is issued:
   selects the in-place NCCL all-gather through ``torch.distributed`` instead;
 * weight decay + scaled update of all ``world_size`` parameters of a round is one multi-tensor
   kernel (``fm_update_multi``) instead of ``2 * world_size`` launches, enqueued on a second
-  stream so that this HBM-bound pass runs under the tensor-core work of the following rounds.
+  stream so that this HBM-bound pass runs under the tensor-core work of the following rounds;
+* with the copy-engine exchange the OWNER applies decay + update to its replica and pushes the
+  updated parameter into the replicas of its peers, instead of every rank gathering and applying
+  every update: replicas are bit-identical before the step and the update is deterministic, so
+  the result is the same, but a rank streams only its share of the parameters through HBM
+  (``FM_MUON_EXCHANGE=updates`` keeps the gather of updates);
+* with ``world_size == 1`` and no hooks the whole step is one C call (``fm_muon_step``), which
+  does the stream and event bookkeeping of the round loop inside the library
+  (``FM_MUON_NATIVE=0`` keeps the loop below).
 """
 from __future__ import annotations
 
