@@ -112,14 +112,30 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- reference arm
-def cpu_reference_sample(threads: int):
-    """The oracle (CPU restatement of flash_muon/muon.py) on two matrices of the workload:
-    one k/v projection [1024x4096] and one q/o projection [4096x4096], full per-matrix work of a
-    step (momentum, Nesterov, 5 Newton-Schulz steps, decay + update).  Returns seconds and the
-    cuBLAS-equivalent FLOPs of the sample."""
+SMALL_SAMPLE = [(1024, 4096), (4096, 4096)]
+
+
+def cpu_sample_shapes():
+    """One whole layer (7 of the 224 matrices: 10-15 s on the GPU box's host cores), or, with
+    FM_BENCH_CPU_SAMPLE=small, one k/v and one q/o projection (CPU-only test runs)."""
+    return SMALL_SAMPLE if os.environ.get("FM_BENCH_CPU_SAMPLE", "layer") == "small" else list(LLAMA_LAYER)
+
+
+def describe_sample(shapes, scale: float) -> str:
+    if shapes == list(LLAMA_LAYER):
+        return (f"oracle port on the host cores: the full Muon.step work of one of the {N_LAYERS} identical "
+                f"layers (7 matrices), extrapolated x{scale:.1f}")
+    return ("oracle port on the host cores: Muon.step work of " + " and ".join(f"one [{r}x{c}]" for r, c in shapes)
+            + f" matrix, scaled to the {len(LLAMA_LAYER) * N_LAYERS}-matrix set by cuBLAS-equivalent FLOPs (x{scale:.1f})")
+
+
+def cpu_reference_sample(threads: int, shapes=None):
+    """The oracle (CPU restatement of flash_muon/muon.py) on a bounded sample of the workload, full
+    per-matrix work of a step (momentum, Nesterov, 5 Newton-Schulz steps, decay + update).
+    Returns seconds and the cuBLAS-equivalent FLOPs of the sample."""
     from oracle import muon_oracle as O
     torch.set_num_threads(threads)
-    shapes = [(1024, 4096), (4096, 4096)]
+    shapes = cpu_sample_shapes() if shapes is None else shapes
     g = torch.Generator().manual_seed(0)
     params = [(torch.randn(*s, generator=g) * 0.02).bfloat16() for s in shapes]
     grads = [(torch.randn(*s, generator=g) * 1e-3).bfloat16() for s in shapes]
@@ -143,22 +159,25 @@ def run_reference(args):
         return
     threads = os.cpu_count() or 1
     _, full = full_step_flops()
+    shapes = cpu_sample_shapes()
     times = []
-    for i in range(args.warmup + args.steps):
-        dt, fl = cpu_reference_sample(threads)
-        if i >= args.warmup:
-            times.append(dt)
+    for _ in range(args.warmup):             # warm-up on the small sample: threads, allocator
+        cpu_reference_sample(threads, SMALL_SAMPLE)
+    for _ in range(args.steps):
+        dt, fl = cpu_reference_sample(threads, shapes)
+        times.append(dt)
     per_sample = sum(times) / len(times)
     est_ms = per_sample * (full / fl) * 1e3
-    sample = ("oracle port on CPU: Muon.step work of one [1024x4096] and one [4096x4096] matrix per "
-              f"step, scaled to the 224-matrix set by cuBLAS-equivalent FLOPs (x{full / fl:.1f})")
+    sample = describe_sample(shapes, full / fl)
     line = {
         "impl": "reference", "metric": "muon_step_ms", "value": est_ms, "unit": "ms",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": est_ms,
         "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": "Muon.step on Llama-3-8B-shaped matrices (BASELINE configs[4])",
-                   "matrices": len(LLAMA_LAYER) * N_LAYERS, "ns_steps": 5, "device": "host cores"},
+                   "layers": N_LAYERS, "matrices": len(LLAMA_LAYER) * N_LAYERS,
+                   "elements": sum(a * b for a, b in LLAMA_LAYER) * N_LAYERS, "ns_steps": HP["ns_steps"],
+                   "parallelism": "host threads", "device": "host cores"},
         "cpu_baseline": {"value": est_ms, "unit": "ms", "cores": threads, "kind": "port",
                          "sample": sample, "sample_seconds": per_sample},
         "e2e": {"value": est_ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -373,12 +392,11 @@ def run_ours(args):
         line["muon_step_ms_gpt2_medium_shapes"] = e0.elapsed_time(e1) / 10
         del gp, gopt
         threads = os.cpu_count() or 1
+        cpu_reference_sample(threads, SMALL_SAMPLE)   # warm the host threads
         dt, fl = cpu_reference_sample(threads)
         line["cpu_baseline"] = {
             "value": dt * (full / fl) * 1e3, "unit": "ms", "cores": threads, "kind": "port",
-            "sample": ("oracle port: Muon.step work of one [1024x4096] and one [4096x4096] matrix, "
-                       f"scaled to the 224-matrix set by cuBLAS-equivalent FLOPs (x{full / fl:.1f})"),
-            "sample_seconds": dt}
+            "sample": describe_sample(cpu_sample_shapes(), full / fl), "sample_seconds": dt}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if ws > 1:

@@ -1,6 +1,7 @@
 """The parts of bench.py that run without a GPU: the reference arm's JSON line and the FLOP /
 byte bookkeeping the roofline figures are computed from."""
 import json
+import os
 import subprocess
 import sys
 from pathlib import Path
@@ -12,7 +13,8 @@ import bench  # noqa: E402
 
 def test_reference_arm_prints_one_json_line():
     out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1",
-                          "--warmup", "0"], capture_output=True, text=True, timeout=600)
+                          "--warmup", "1"], capture_output=True, text=True, timeout=600,
+                         env={**os.environ, "FM_BENCH_CPU_SAMPLE": "small"})  # two matrices, not a layer
     assert out.returncode == 0, out.stderr
     lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
     assert len(lines) == 1
@@ -20,7 +22,17 @@ def test_reference_arm_prints_one_json_line():
     assert d["impl"] == "reference" and d["metric"] == "muon_step_ms" and d["unit"] == "ms"
     assert d["higher_is_better"] is False and d["value"] > 0
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert "scaled" in d["cpu_baseline"]["sample"] and d["cpu_baseline"]["sample_seconds"] > 0
     assert d["e2e"] == {"value": d["value"], "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+
+
+def test_default_cpu_sample_is_one_whole_layer():
+    shapes = bench.cpu_sample_shapes()
+    assert shapes == list(bench.LLAMA_LAYER) and len(shapes) == 7
+    _, full = bench.full_step_flops()
+    fl = sum(bench.ns_flops(*s)[1] for s in shapes)
+    assert abs(full / fl - bench.N_LAYERS) < 1e-9          # the extrapolation is exactly x32
+    assert "x32.0" in bench.describe_sample(shapes, full / fl)
 
 
 def test_flop_bookkeeping_matches_the_survey_figures():
