@@ -14,6 +14,7 @@ struct GemmParams {
   int tiles_m;    // row tiles of the schedule
   int num_tiles;  // length of the static tile list
   int num_kb;     // ceil(K / 64)
+  int strip_w;    // CTA-pair kernel, symmetric lists: width of the column strips (0: column order)
   const void* D;  // optional addend, row-major, unit column stride
   long long ldd;
   void* C;        // direct output (may be null): C[r*ldc_r + c*ldc_c]

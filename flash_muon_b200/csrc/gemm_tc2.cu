@@ -357,6 +357,19 @@ SkScratch* sk_acquire(cudaStream_t stream) {
   return &s;
 }
 
+// Tile order of a symmetric list: FM_GEMM_STRIP=<w> selects column strips of width w
+// (tile_schedule.cuh has the reasoning: fewer distinct panels per wave, hence fewer DRAM reads,
+// once the triangle has more than ~16 tile columns).  The default stays the column order: on
+// B200 the 8192^2 and 16384 x 8192 products ran at the same speed in both orders (they are bound
+// by the tensor pipe, not by DRAM), and the DRAM traffic of the strip order has not been profiled.
+int strip_width(const GemmParams& p) {
+  if (!p.sym) return 0;
+  const char* e = getenv("FM_GEMM_STRIP");
+  if (e == nullptr) return 0;
+  const int w = atoi(e);
+  return (w > 0 && w <= 64) ? w : 0;
+}
+
 bool sk_enabled() {
   const char* e = getenv("FM_GEMM_BALANCE");  // read per call: lets one process compare both
   return !(e && atoi(e) == 0);
@@ -458,6 +471,7 @@ int gemm_tc2_launch(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB, G
                     cudaStream_t stream) {
   p.tiles_m = (p.M + 255) / 256;
   p.num_tiles = gemm_tc2_tiles(p.M, p.N, p.sym);
+  p.strip_w = strip_width(p);
   const int max_pairs = gemm_tc2_max_pairs(dtype);
   if (max_pairs <= 0) return fail(FM_ERR_CUDA, "no resident CTA pair possible for the GEMM kernel");
   return dtype == FM_BF16 ? launch2<__nv_bfloat16>(tmA, tmB, p, max_pairs, stream)

@@ -3,7 +3,7 @@
 // computed exactly once (tests/schedule_check.cpp does; it includes this file with a plain C++
 // compiler).  The functions are templated on the parameter struct: the kernels pass GemmParams,
 // a host check passes any struct with the same schedule fields
-//   M, N, sym, tiles_m, num_tiles, num_kb, sk_dp_tiles, sk_per, sk_total.
+//   M, N, sym, tiles_m, num_tiles, num_kb, strip_w, sk_dp_tiles, sk_per, sk_total.
 #pragma once
 #include <math.h>
 
@@ -87,6 +87,20 @@ FM_HD int count_tiles2(long long M, long long N, int sym) {
   return (int)(sym ? tn * (tn + 1) / 2 : tm * tn);
 }
 
+// Symmetric lists come in two orders.  strip_w == 0: column by column, rows 0..j inside column
+// j.  strip_w == w > 0: strips of w tile columns; inside a strip row by row (i = 0 .. last
+// column of the strip), inside a row the strip's columns j >= i.  The CTA pairs of a launch work
+// on consecutive tiles at the same time and advance through K in step, so what a "wave" of them
+// reads from DRAM is one K sweep of every distinct 256-row panel its tiles touch, as row or as
+// column.  P consecutive tiles of the column order touch about j + P / j panels around column j
+// (all 32 of an 8192-row matrix in the last waves); P consecutive tiles of a strip touch about
+// w + P / w, e.g. 17 for w = 8 and 74 pairs.
+template <class P>
+FM_HD long long strip_tiles_before(const P& p, int s) {
+  const long long w = p.strip_w;
+  return w * w * s * (s - 1) / 2 + (long long)s * w * (w + 1) / 2;
+}
+
 template <class P>
 FM_HD Tile2 decode_tile2(const P& p, int t) {
   Tile2 o;
@@ -95,6 +109,30 @@ FM_HD Tile2 decode_tile2(const P& p, int t) {
     const int tm = t - tn * p.tiles_m;
     o.m0 = tm * 256;
     o.n0 = tn * 256;
+  } else if (p.strip_w > 0) {
+    const int w = p.strip_w;
+    int s = 0;
+    while (strip_tiles_before(p, s + 1) <= t) ++s;      // a handful of strips
+    const int c0 = s * w;
+    const int n = p.tiles_m;                            // tile rows = tile columns
+    const int wc = (c0 + w <= n) ? w : (n - c0);        // only the last strip can be narrower
+    int r = t - (int)strip_tiles_before(p, s);
+    int i, j;
+    if (r < c0 * wc) {                                  // rows above the strip's diagonal block
+      i = r / wc;
+      j = c0 + (r - i * wc);
+    } else {                                            // the triangle on the diagonal
+      r -= c0 * wc;
+      int ii = 0;
+      while (r >= wc - ii) {
+        r -= wc - ii;
+        ++ii;
+      }
+      i = c0 + ii;
+      j = i + r;
+    }
+    o.m0 = i * 256;
+    o.n0 = j * 256;
   } else {
     int j = (int)((sqrtf(8.f * (float)t + 1.f) - 1.f) * 0.5f);
     while ((long long)(j + 1) * (j + 2) / 2 <= t) ++j;

@@ -8,7 +8,8 @@
 //   1. single-CTA lists (128 x 128 and 128 x 256 tiles), general and symmetric: every 128 x 128
 //      output block that has to be computed is covered by exactly one tile, no block below the
 //      diagonal of a symmetric product is covered, every tile lies inside the matrix;
-//   2. CTA-pair lists (256 x 256 tiles): the same with 256-blocks;
+//   2. CTA-pair lists (256 x 256 tiles): the same with 256-blocks, in the column order and in
+//      column strips of several widths;
 //   3. the balanced tail: over all pairs every (tile, K block) is computed exactly once; a pair
 //      deposits at most once and before it gathers; the deposits a finishing pair adds up are
 //      exactly those of pairs c_first .. pair-1 (the rule the kernel uses to find them), and the
@@ -24,7 +25,7 @@
 namespace {
 
 struct Sched {
-  int M, N, sym, tiles_m, num_tiles, num_kb, sk_dp_tiles, sk_per;
+  int M, N, sym, tiles_m, num_tiles, num_kb, strip_w, sk_dp_tiles, sk_per;
   long long sk_total;
 };
 
@@ -73,9 +74,9 @@ void check_single(int M, int N, int sym) {
   ++g_checked;
 }
 
-void check_pair_list(int M, int N, int sym) {
+void check_pair_list(int M, int N, int sym, int strip_w = 0) {
   Sched p{};
-  p.M = M; p.N = N; p.sym = sym;
+  p.M = M; p.N = N; p.sym = sym; p.strip_w = strip_w;
   p.tiles_m = (M + 255) / 256;
   p.num_tiles = fm::count_tiles2(M, N, sym);
   const int bn = (N + 255) / 256;
@@ -185,6 +186,7 @@ int main() {
         check_single<128>(m, m, 1);
         check_single<256>(m, m, 1);
         check_pair_list(m, m, 1);
+        for (int w : {1, 2, 3, 5, 8, 12, 64}) check_pair_list(m, m, 1, w);   // column strips
       } else {
         for (int n : dims) {
           if ((long long)m * n > 8192LL * 16384) continue;

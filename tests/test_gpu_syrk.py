@@ -136,6 +136,22 @@ def test_balanced_tail_schedule(monkeypatch):
     _lib.device_status()
 
 
+@pytest.mark.parametrize("w", [3, 8])
+def test_strip_tile_order_gives_the_same_product(w, monkeypatch):
+    """FM_GEMM_STRIP walks the same tiles in column strips: with whole tiles (short K, no balanced
+    tail) every tile is computed by the same instructions, so the product is bit-identical."""
+    torch.manual_seed(4)
+    x = (torch.randn(4700, 320, device=DEV) / 18).bfloat16()     # 19 tile columns, ragged edge
+    monkeypatch.setenv("FM_GEMM_IMPL", "2")
+    monkeypatch.setenv("FM_GEMM_STRIP", "0")
+    y0 = fm.matmul_transpose(x)
+    monkeypatch.setenv("FM_GEMM_STRIP", str(w))
+    y1 = fm.matmul_transpose(x)
+    assert torch.equal(y0, y1) and torch.equal(y1, y1.T)
+    assert rel_fro(y1, x.float() @ x.float().T) <= 1e-2
+    _lib.device_status()
+
+
 def test_empty_and_degenerate():
     assert fm.matmul_transpose(torch.empty(0, 16, device=DEV, dtype=torch.bfloat16)).shape == (0, 0)
     y = fm.matmul_transpose(torch.empty(5, 0, device=DEV, dtype=torch.bfloat16))
