@@ -147,6 +147,21 @@ def cpu_reference_sample(threads: int, shapes=None):
     return dt, flops
 
 
+def replica_checksum(params) -> torch.Tensor:
+    """Two int64 words over the raw bits of all parameters (sum, and sum weighted by position
+    within each tensor's 64Ki-element blocks): equal on two ranks iff, to all practical purposes,
+    their replicas are bit-identical."""
+    acc = torch.zeros(2, dtype=torch.int64, device=params[0].device)
+    for i, p in enumerate(params):
+        bits = p.detach().reshape(-1).view(torch.int16 if p.element_size() == 2 else torch.int32)
+        acc[0] += bits.sum(dtype=torch.int64) * (i + 1)
+        n = bits.numel() - bits.numel() % 65536
+        if n:
+            blocks = bits[:n].view(-1, 65536).sum(dim=0, dtype=torch.int64)
+            acc[1] += (blocks * torch.arange(1, 65537, device=bits.device, dtype=torch.int64)).sum() * (i + 1)
+    return acc
+
+
 def full_step_flops():
     alg = sum(ns_flops(*s)[0] for s in LLAMA_LAYER) * N_LAYERS
     full = sum(ns_flops(*s)[1] for s in LLAMA_LAYER) * N_LAYERS
@@ -338,6 +353,19 @@ def run_ours(args):
     sync()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / k2)
 
+    # outside every timed region: after all those steps the replicas must still be bit-identical
+    # on every rank (flash_muon/muon.py:84-89 applies every update on every rank)
+    replicas_identical = None
+    if ws > 1:
+        try:  # a failed check is reported as null, it never costs the measurement
+            h = replica_checksum(params).to(dev)
+            lo, hi = h.clone(), h.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            replicas_identical = bool(torch.equal(lo, hi))
+        except Exception as exc:  # noqa: BLE001
+            print(f"replica check failed to run: {exc}", file=sys.stderr, flush=True)
+
     # launches of this library's kernels per step on this rank: per owned matrix 1 momentum,
     # 2 normalisation, 3 GEMMs per Newton-Schulz step; per round one multi-tensor update, or one
     # update per owned matrix when owners push updated parameters to their peers
@@ -362,6 +390,7 @@ def run_ours(args):
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": k2, "note": "per rank: owned gradients from pinned host memory, owned parameters back to pinned host memory; copies are streamed per parameter through Muon.step(grad_ready=, on_applied=) and all lie inside the timed region"},
         "gpu_launches": launches_per_step * args.steps,
+        "replicas_identical": replicas_identical,
         "clocks": clocks,
     }
     if rank == 0:

@@ -42,3 +42,18 @@ def test_flop_bookkeeping_matches_the_survey_figures():
     a, f = bench.ns_flops(4096, 4096)
     assert abs(a - 1.3746e12) / 1.3746e12 < 1e-3 and abs(f - 2.0616e12) / 2.0616e12 < 1e-3
     assert sum(r * c for r, c in bench.LLAMA_LAYER) * bench.N_LAYERS == 6979321856
+
+
+def test_replica_checksum_sees_single_bit_and_position_changes():
+    import torch
+    g = torch.Generator().manual_seed(0)
+    params = [torch.randn(300, 500, generator=g).bfloat16(), torch.randn(64, 64, generator=g)]
+    base = bench.replica_checksum(params)
+    assert torch.equal(base, bench.replica_checksum([p.clone() for p in params]))
+    flipped = [p.clone() for p in params]
+    flipped[0].view(torch.int16)[17, 33] ^= 1
+    assert not torch.equal(base, bench.replica_checksum(flipped))
+    swapped = [p.clone() for p in params]
+    a, b = swapped[0].view(-1)[5].clone(), swapped[0].view(-1)[70000].clone()
+    swapped[0].view(-1)[5], swapped[0].view(-1)[70000] = b, a
+    assert a != b and not torch.equal(base, bench.replica_checksum(swapped))
