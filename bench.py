@@ -13,13 +13,20 @@ rank 0 at N=1 and rides in the same JSON line (`matmul_transpose`, `roofline`).
 The line also carries: `e2e` (same step with gradients coming from pinned host memory and the
 owned parameters copied back, copies inside the timed region), `cpu_baseline` (the oracle's CPU
 restatement of the reference on the box's host cores, bounded sample), `clocks` (nvidia-smi
-samples taken during the timed region) and `gpu_launches`.
+samples taken during the timed region), `gpu_launches`, and `params_checksum`: after the timed
+legs every rank resets parameters, momentum and gradients to seeded values, takes two steps and
+hashes the raw bits of all parameters -- the same two words at every N are the world-size
+invariance of flash_muon/muon.py:84-89, visible from outside.  At N=1 the line adds the rest of
+BASELINE.json's configs: the matmul_transpose sweep of configs[2] against cuBLAS, configs[1]
+(fast_newtonschulz 4096^2), the HBM-bound kernels against the measured copy bandwidth, the
+GPT-2-medium-shaped step of configs[3] and the same Llama-shaped step in plain torch CUDA ops.
 
 Data is synthetic (seeded normal values of the shapes above); no dataset is involved.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -201,6 +208,34 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------- our arm
+GEMM_SOURCES = ["gemm_tc2.cu", "gemm_common.cuh", "tile_schedule.cuh", "ptx.cuh"]
+
+
+def gemm_source_hash() -> str:
+    h = hashlib.sha256()
+    for name in GEMM_SOURCES:
+        h.update((ROOT / "flash_muon_b200" / "csrc" / name).read_bytes())
+    return h.hexdigest()[:16]
+
+
+def recorded_traffic(m: int, k: int):
+    """DRAM bytes per launch of the symmetric product from the ncu capture summarised under
+    profiles/ -- only if that capture was taken from the kernel sources this run uses and no
+    tuning switch is set; otherwise null (a stale figure next to a fresh timing says nothing)."""
+    f = ROOT / "profiles" / "gemm_tc2_kernel_syrk_traffic.json"
+    if not f.exists():
+        return None, "no capture recorded"
+    rec = json.loads(f.read_text())
+    if [m, k] != rec.get("shape"):
+        return None, "no capture for this shape"
+    if rec.get("source_hash") != gemm_source_hash():
+        return None, f"capture {rec.get('commit')} predates the current kernel sources"
+    if any(os.environ.get(v) for v in ("FM_GEMM_IMPL", "FM_GEMM_BN", "FM_GEMM_STAGES", "FM_GEMM_BALANCE",
+                                       "FM_GEMM_STRIP", "FM_PDL")):
+        return None, "tuning switches set"
+    return rec["dram_bytes_read"] + rec["dram_bytes_written"], f"{rec['summary']} (commit {rec['commit']})"
+
+
 def time_syrk(peaks, dim=SYRK_DIM, reps=30):
     """matmul_transpose at dim^2 bf16 (8192 by default) on the current device, against cuBLAS
     x @ x.T interleaved in the same process.  Input + output (268 MB at 8192) exceed L2, so no
@@ -233,13 +268,119 @@ def time_syrk(peaks, dim=SYRK_DIM, reps=30):
     res = {"shape": [m, k], "ms": t, "tflops_effective": 2 * m * m * k / t / 1e9,
            "tflops_algorithmic": alg / t / 1e9, "tflops_executed": execd / t / 1e9,
            "cublas_ms": tc, "speedup_vs_cublas": tc / t, "reps": reps}
-    # DRAM bytes of one 8192^2 launch: dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture
-    traffic = 692.8e6 + 131.2e6 if m == 8192 else None
+    traffic, traffic_source = recorded_traffic(m, k)
     roof = {"kernel": f"gemm_tc2_kernel<bf16> as matmul_transpose {m}x{k}", "bound": "tensor",
             "achieved": alg / t / 1e9, "peak": peaks["bf16"], "unit": "TFLOP/s",
             "frac": alg / t / 1e9 / peaks["bf16"], "frac_executed": execd / t / 1e9 / peaks["bf16"],
-            "traffic": traffic, "peak_source": f"{peaks['source']} burst (kernel timed alone)"}
+            "traffic": traffic, "traffic_source": traffic_source,
+            "algorithmic_bytes": 2 * m * k + 2 * m * m,
+            "peak_source": f"{peaks['source']} burst (kernel timed alone)"}
     return res, roof
+
+
+def cuda_time(fn, warm, rep):
+    """ms per call: `warm` untimed calls, then `rep` back-to-back calls between two CUDA events
+    (the protocol of the reference's benchmark.py:69-79)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(rep):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / rep
+
+
+def sweep_config2(peaks):
+    """BASELINE configs[2]: matmul_transpose in bf16, entries N(0,1)/sqrt(k), four squares and two
+    rectangles (the tall one transposed first, as in Muon), against cuBLAS `x @ x.T` in the same
+    process, alternating; warm-up 25, 100 reps."""
+    import flash_muon_b200 as fm
+    out = []
+    for m, k in [(1024, 1024), (2048, 2048), (4096, 4096), (8192, 8192), (4096, 16384), (16384, 4096)]:
+        x = (torch.randn(m, k, device="cuda") / k ** 0.5).bfloat16()
+        if m > k:
+            x = x.T.contiguous()
+        mm, kk = x.shape
+        y = torch.empty(mm, mm, device="cuda", dtype=torch.bfloat16)
+        ours, cub = [], []
+        for _ in range(2):
+            ours.append(cuda_time(lambda: fm.matmul_transpose_assign(x, y), 25, 100))
+            cub.append(cuda_time(lambda: torch.matmul(x, x.T, out=y), 25, 100))
+        t, tc = min(ours), min(cub)
+        alg = mm * (mm + 1) * kk
+        out.append({"shape": [m, k], "ms": t, "tflops_algorithmic": alg / t / 1e9,
+                    "frac_of_peak": alg / t / 1e9 / peaks["bf16"], "cublas_ms": tc,
+                    "speedup_vs_cublas": tc / t})
+        del x, y
+    return out
+
+
+def time_config1(peaks):
+    """BASELINE configs[1]: fast_newtonschulz, 5 steps, 4096 x 4096 bf16."""
+    import flash_muon_b200 as fm
+    G = torch.randn(4096, 4096, device="cuda").bfloat16()
+    out = torch.empty_like(G)
+    ws = torch.empty(fm.newtonschulz_workspace_bytes(4096, 4096), device="cuda", dtype=torch.uint8)
+    t = min(cuda_time(lambda: fm.fast_newtonschulz(G, 5, out=out, workspace=ws), 10, 50) for _ in range(2))
+    alg, full = ns_flops(4096, 4096)
+    return {"shape": [4096, 4096], "steps": 5, "ms": t, "tflops_algorithmic": alg / t / 1e9,
+            "tflops_cublas_equivalent": full / t / 1e9,
+            "frac_of_sustained_peak": alg / t / 1e9 / peaks["bf16_sustained"]}
+
+
+def time_hbm_kernels(peaks):
+    """The HBM-bound kernels alone on 2^28 bf16 elements (512 MB per tensor, far beyond L2),
+    algorithmic bytes per element over the CUDA-event time, against the measured copy bandwidth."""
+    import ctypes
+    from flash_muon_b200._lib import lib, check
+    n = 1 << 28
+    rows, cols = 16384, 16384
+    g = (torch.randn(n, device="cuda") * 1e-3).bfloat16()
+    b = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    p = (torch.randn(n, device="cuda") * 0.02).bfloat16()
+    xd = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    xt = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    part = torch.empty(lib.fm_norm_scratch_floats(), device="cuda", dtype=torch.float32)
+    ptrs, upds = (ctypes.c_void_p * 1)(p.data_ptr()), (ctypes.c_void_p * 1)(g.data_ptr())
+    nels, alphas = (ctypes.c_int64 * 1)(n), (ctypes.c_double * 1)(-0.02)
+    cases = {
+        "momentum_nesterov": (8, lambda: check(lib.fm_momentum(g.data_ptr(), b.data_ptr(), n, 0, 0.95, 1, None, 0))),
+        "momentum_nesterov_with_norm_partials": (8, lambda: check(lib.fm_momentum(
+            g.data_ptr(), b.data_ptr(), n, 0, 0.95, 1, part.data_ptr(), 0))),
+        "decay_update": (6, lambda: check(lib.fm_update_multi(ptrs, upds, nels, alphas, 1, 0, 0.9998, 0))),
+        "normalize_with_transpose": (8, lambda: check(lib.fm_normalize(
+            g.data_ptr(), rows, cols, cols, 0, xd.data_ptr(), cols, xt.data_ptr(), rows, part.data_ptr(), 0))),
+    }
+    out = {}
+    for name, (bytes_per_elem, fn) in cases.items():
+        t = min(cuda_time(fn, 3, 10) for _ in range(2))
+        gbs = bytes_per_elem * n / t / 1e6
+        out[name] = {"ms": t, "bytes_per_element": bytes_per_elem, "gb_s": gbs,
+                     "frac_of_hbm": gbs / peaks["hbm_gbs"]}
+    out["elements"] = n
+    return out
+
+
+def time_torch_cuda_step():
+    """The same Llama-shaped step in plain torch CUDA ops (cuBLAS products and torch's element
+    kernels, the formulation of flash_muon/muon.py with `x @ x.T` for the symmetric products): one
+    of the 32 identical layers, twice, the second timed, x32."""
+    from oracle import muon_oracle as O
+    g = torch.Generator(device="cuda").manual_seed(2)
+    params = [(torch.randn(*s, device="cuda", generator=g) * 0.02).bfloat16() for s in LLAMA_LAYER]
+    grads = [(torch.randn(*s, device="cuda", generator=g) * 1e-3).bfloat16() for s in LLAMA_LAYER]
+    bufs = {}
+    O.muon_step(params, [x.clone() for x in grads], bufs, world_size=1, native=True, **HP)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    O.muon_step(params, grads, bufs, world_size=1, native=True, **HP)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * N_LAYERS
 
 
 def run_ours(args):
@@ -311,7 +452,9 @@ def run_ours(args):
         for i, p in enumerate(grp["params"]):
             if i % ws == rank:
                 owned.append(p)
-    host_g = {s: (torch.randn(*s) * 1e-3).bfloat16().pin_memory() for s in set(LLAMA_LAYER)}
+    hg = torch.Generator().manual_seed(4321)      # same host gradients on every rank
+    host_g = {s: (torch.randn(*s, generator=hg) * 1e-3).bfloat16().pin_memory()
+              for s in sorted(set(LLAMA_LAYER))}
     host_p = {s: torch.empty(*s, dtype=torch.bfloat16).pin_memory() for s in set(LLAMA_LAYER)}
     h2d = sum(p.numel() * 2 for p in owned)
     d2h = h2d
@@ -353,25 +496,52 @@ def run_ours(args):
     sync()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / k2)
 
-    # outside every timed region: after all those steps the replicas must still be bit-identical
-    # on every rank (flash_muon/muon.py:84-89 applies every update on every rank)
-    replicas_identical = None
-    if ws > 1:
-        try:  # a failed check is reported as null, it never costs the measurement
-            h = replica_checksum(params).to(dev)
+    # Outside every timed region: parameters, momentum and gradients go back to seeded values,
+    # two more steps run, and the raw bits of all parameters are hashed.  Every update reaches
+    # every replica (flash_muon/muon.py:84-89), so the two words are the same on every rank and
+    # at every world size.
+    replicas_identical, params_checksum = None, None
+    try:  # a failed check is reported as null, it never costs the measurement
+        sync()
+        cg = torch.Generator(device=dev).manual_seed(7)
+        for p in params:
+            p.data.copy_((torch.randn(p.shape, device=dev, generator=cg) * 0.02).bfloat16())
+            p.grad.copy_((torch.randn(p.shape, device=dev, generator=cg) * 1e-3).bfloat16())
+            st = opt.state.get(p)
+            if st and "momentum_buffer" in st:
+                st["momentum_buffer"].zero_()
+        sync()
+        for _ in range(2):
+            opt.step()
+        sync()
+        h = replica_checksum(params).to(dev)
+        params_checksum = [int(v) for v in h.tolist()]
+        if ws > 1:
             lo, hi = h.clone(), h.clone()
             dist.all_reduce(lo, op=dist.ReduceOp.MIN)
             dist.all_reduce(hi, op=dist.ReduceOp.MAX)
             replicas_identical = bool(torch.equal(lo, hi))
-        except Exception as exc:  # noqa: BLE001
-            print(f"replica check failed to run: {exc}", file=sys.stderr, flush=True)
+    except Exception as exc:  # noqa: BLE001
+        print(f"replica check failed to run: {exc}", file=sys.stderr, flush=True)
 
     # launches of this library's kernels per step on this rank: per owned matrix 1 momentum,
     # 2 normalisation, 3 GEMMs per Newton-Schulz step; per round one multi-tensor update, or one
     # update per owned matrix when owners push updated parameters to their peers
     rounds = sum((len(grp["params"]) + ws - 1) // ws for grp in opt.param_groups)
-    pushes_params = bool(getattr(opt, "_peer", None)) and os.environ.get("FM_MUON_EXCHANGE", "params") != "updates"
-    launches_per_step = len(owned) * (1 + 2 + 3 * HP["ns_steps"]) + (len(owned) if pushes_params else rounds)
+    pushes_params = bool(getattr(opt, "_peer", None)) and getattr(opt, "_push_params", False) and \
+        os.environ.get("FM_MUON_EXCHANGE", "params") != "updates"
+    if ws == 1:
+        # single-call step: per Newton-Schulz pass (a batch of narrow matrices, or one matrix)
+        # 1 momentum, 1 normalisation, 3 GEMMs per iteration, 1 decay + update
+        launches_per_step = 0
+        for grp in opt.param_groups:
+            batch = min(opt._plan(grp, True)[1], len(grp["params"]))
+            passes = -(-len(grp["params"]) // batch)
+            launches_per_step += passes * (1 + 1 + 3 * HP["ns_steps"] + 1)
+    else:
+        # round loop: per owned matrix 1 momentum, 1 normalisation, 3 GEMMs per iteration; one
+        # decay + update per owned matrix (owners push parameters) or per round
+        launches_per_step = len(owned) * (1 + 1 + 3 * HP["ns_steps"]) + (len(owned) if pushes_params else rounds)
     alg, full = full_step_flops()
     alg, full = alg * args.layers / N_LAYERS, full * args.layers / N_LAYERS
 
@@ -384,13 +554,16 @@ def run_ours(args):
                    "ns_steps": HP["ns_steps"], "parallelism": f"dp{ws} round-robin ownership",
                    "exchange": ("none" if ws == 1 else "owners push updated parameters (DMA)" if pushes_params
                                 else "all-gather of updates"),
-                   "l2": "working set (42+ GB) far larger than L2; no flush needed"},
+                   "l2": "working set (42+ GB) far larger than L2; no flush needed",
+                   "gradients": "seeded N(0, 1e-3) once; not regenerated between timed steps (the "
+                                "timing does not depend on the values; Nesterov rewrites p.grad in place)"},
         "step_tflops_algorithmic": alg / ms / 1e9, "step_tflops_cublas_equivalent": full / ms / 1e9,
         "step_frac_of_sustained_peak": alg / ms / 1e9 / ws / peaks["bf16_sustained"],
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": k2, "note": "per rank: owned gradients from pinned host memory, owned parameters back to pinned host memory; copies are streamed per parameter through Muon.step(grad_ready=, on_applied=) and all lie inside the timed region"},
         "gpu_launches": launches_per_step * args.steps,
         "replicas_identical": replicas_identical,
+        "params_checksum": params_checksum,
         "clocks": clocks,
     }
     if rank == 0:
@@ -420,6 +593,13 @@ def run_ours(args):
         torch.cuda.synchronize()
         line["muon_step_ms_gpt2_medium_shapes"] = e0.elapsed_time(e1) / 10
         del gp, gopt
+        torch.cuda.empty_cache()
+        line["matmul_transpose_sweep"] = sweep_config2(peaks)
+        line["fast_newtonschulz_4096"] = time_config1(peaks)
+        line["hbm_kernels"] = time_hbm_kernels(peaks)
+        torch.cuda.empty_cache()
+        line["torch_cuda_step_ms"] = time_torch_cuda_step()
+        torch.cuda.empty_cache()
         threads = os.cpu_count() or 1
         cpu_reference_sample(threads, SMALL_SAMPLE)   # warm the host threads
         dt, fl = cpu_reference_sample(threads)
@@ -430,6 +610,8 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if ws > 1:
         dist.barrier()
+        if "opt" in locals():
+            opt.close()
         dist.destroy_process_group()
 
 

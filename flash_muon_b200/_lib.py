@@ -16,7 +16,7 @@ LIB_PATH = Path(os.environ.get("FLASH_MUON_B200_LIB", _PKG_DIR / "libflash_muon_
 
 FM_OK = 0
 FM_BF16, FM_F16, FM_F32 = 0, 1, 2
-FM_NS_FAITHFUL, FM_NS_PRECISE = 0, 1
+FM_NS_FAITHFUL, FM_NS_PRECISE, FM_NS_SUMSQ_READY = 0, 1, 2
 
 _DTYPES = {torch.bfloat16: FM_BF16, torch.float16: FM_F16, torch.float32: FM_F32}
 
@@ -30,6 +30,7 @@ class MuonGroup(ctypes.Structure):
                 ("cols", ctypes.POINTER(c_int64)), ("alphas", ctypes.POINTER(c_double)),
                 ("count", ctypes.c_int32), ("p_dtype", ctypes.c_int32), ("g_dtype", ctypes.c_int32),
                 ("nesterov", ctypes.c_int32), ("ns_steps", ctypes.c_int32), ("lanes", ctypes.c_int32),
+                ("batch", ctypes.c_int32), ("reserved", ctypes.c_int32),
                 ("momentum_coef", c_double), ("decay", c_double),
                 ("slots", ctypes.POINTER(c_void_p))]
 
@@ -39,14 +40,24 @@ SIGNATURES = {
     "fm_version": (c_int, []),
     "fm_last_error": (ctypes.c_char_p, []),
     "fm_device_status": (c_int, [ctypes.POINTER(ctypes.c_uint)]),
+    "fm_set_option": (c_int, [ctypes.c_char_p, c_int]),
+    "fm_get_option": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_int)]),
+    "fm_syrk_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),
     "fm_syrk": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int,
-                        c_void_p]),
+                        c_void_p, c_size_t, c_void_p]),
     "fm_gemm_nt": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64,
                            c_void_p, c_int64, c_float, c_float, c_void_p, c_int64, c_void_p,
                            c_int64, c_int, c_int, c_void_p]),
     "fm_syrk_poly": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_float,
                              c_float, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "fm_ns_workspace_bytes": (c_size_t, [c_int64, c_int64]),
+    "fm_ns_partials_offset": (c_size_t, [c_int64, c_int64]),
+    "fm_ns_batched_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64]),
+    "fm_ns_batched_partials_offset": (c_size_t, [c_int, c_int64, c_int64]),
+    "fm_newtonschulz_batched": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64),
+                                        ctypes.POINTER(c_int64), c_int, c_int, c_int,
+                                        ctypes.POINTER(c_void_p), c_void_p, c_size_t, c_int,
+                                        c_void_p]),
     "fm_newtonschulz": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p,
                                 c_void_p, c_size_t, c_int, c_void_p]),
     "fm_newtonschulz_static": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p,
@@ -54,7 +65,8 @@ SIGNATURES = {
     "fm_normalize": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_int64,
                              c_void_p, c_int64, c_void_p, c_void_p]),
     "fm_norm_scratch_floats": (c_size_t, []),
-    "fm_momentum": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_double, c_int, c_void_p]),
+    "fm_momentum": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_double, c_int, c_void_p,
+                            c_void_p]),
     "fm_ipc_export": (c_int, [c_void_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_uint64)]),
     "fm_ipc_import": (c_int, [ctypes.c_char_p, ctypes.c_uint64, ctypes.POINTER(c_void_p)]),
     "fm_ipc_close_all": (c_int, []),
@@ -107,6 +119,22 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 def current_stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+on_option_change: list = []  # callbacks of modules that cache plans depending on the options
+
+
+def set_option(name: str, value: int) -> None:
+    """Process-wide tuning switch of the library (``fm_set_option``)."""
+    check(lib.fm_set_option(name.encode(), int(value)))
+    for fn in on_option_change:
+        fn()
+
+
+def get_option(name: str) -> int:
+    v = c_int(0)
+    check(lib.fm_get_option(name.encode(), ctypes.byref(v)))
+    return v.value
 
 
 def device_status() -> int:

@@ -1,6 +1,7 @@
 // Error reporting, device queries and tensor-map encoding shared by the library.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -27,6 +28,37 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 void clear_error() { tl_error[0] = 0; }
+
+Options& options() {
+  static Options opt;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    auto env = [](const char* name, int* dst) {
+      if (const char* e = getenv(name)) *dst = atoi(e);
+    };
+    env("FM_GEMM_IMPL", &opt.gemm_impl);
+    env("FM_GEMM_BN", &opt.gemm_bn);
+    env("FM_GEMM_STAGES", &opt.gemm_stages);
+    env("FM_GEMM_BALANCE", &opt.gemm_balance);
+    env("FM_GEMM_STRIP", &opt.gemm_strip);
+    env("FM_PDL", &opt.pdl);
+  });
+  return opt;
+}
+
+namespace {
+int* option_slot(const char* name) {
+  Options& o = options();
+  if (!name) return nullptr;
+  if (!strcmp(name, "gemm_impl")) return &o.gemm_impl;
+  if (!strcmp(name, "gemm_bn")) return &o.gemm_bn;
+  if (!strcmp(name, "gemm_stages")) return &o.gemm_stages;
+  if (!strcmp(name, "gemm_balance")) return &o.gemm_balance;
+  if (!strcmp(name, "gemm_strip")) return &o.gemm_strip;
+  if (!strcmp(name, "pdl")) return &o.pdl;
+  return nullptr;
+}
+}  // namespace
 
 int sm_count() {
   static int cached[kMaxDevices] = {0};
@@ -93,7 +125,23 @@ int encode_tmap_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner
 
 }  // namespace fm
 
-extern "C" int fm_version(void) { return 100; }
+extern "C" int fm_version(void) { return 200; }
+
+extern "C" int fm_set_option(const char* name, int value) {
+  fm::clear_error();
+  int* slot = fm::option_slot(name);
+  if (!slot) return fm::fail(FM_ERR_INVALID, "unknown option '%s'", name ? name : "(null)");
+  *slot = value;
+  return FM_OK;
+}
+
+extern "C" int fm_get_option(const char* name, int* value) {
+  fm::clear_error();
+  int* slot = fm::option_slot(name);
+  if (!slot || !value) return fm::fail(FM_ERR_INVALID, "unknown option '%s'", name ? name : "(null)");
+  *value = *slot;
+  return FM_OK;
+}
 
 extern "C" const char* fm_last_error(void) { return fm::tl_error; }
 

@@ -34,6 +34,19 @@ unsigned int* device_error_word();
 int encode_tmap_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
                    uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer);
 
+// Process-wide tuning switches (fm_set_option / fm_get_option).  Initial values come from the
+// FM_GEMM_* / FM_PDL environment variables, read once when the library is first used; nothing on
+// a launch path calls getenv.
+struct Options {
+  int gemm_impl = 0;     // 0: by tile count; 1: single-CTA kernel; 2: CTA-pair kernel
+  int gemm_bn = 0;       // single-CTA kernel: 0 by tile count, 128 or 256
+  int gemm_stages = 0;   // CTA-pair kernel: 0 = default ring depth, else 2..7
+  int gemm_balance = 1;  // 0: never cut the tail of a tile list by K blocks
+  int gemm_strip = -1;   // symmetric lists of the pair kernel: -1 by size, 0 column order, w strips
+  int pdl = 1;           // 0: launch the GEMM kernels without programmatic stream serialization
+};
+Options& options();
+
 inline size_t dtype_bytes(int dtype) { return dtype == FM_F32 ? 4 : 2; }
 
 }  // namespace fm

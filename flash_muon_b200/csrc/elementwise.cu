@@ -6,11 +6,16 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "muon_kernels.cuh"
 
 namespace fm {
 namespace {
 
 constexpr int kNormBlocks = 1024;  // upper bound of partial sums (floats of scratch)
+
+__device__ __forceinline__ void ptx_grid_dep_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 template <typename T> __device__ __forceinline__ float ld_f(T v);
 template <> __device__ __forceinline__ float ld_f<float>(float v) { return v; }
@@ -40,13 +45,43 @@ __device__ __forceinline__ float block_sum_256(float v, float* red /* 8 floats *
   return s;
 }
 
+// Matrices of one normalisation launch (blockIdx.y selects one).  `g` is [rows, cols] with row
+// pitch ldg; xd receives the scaled copy in the same orientation, xt its transpose (either may be
+// null); `partials` holds norm_blocks(rows * cols) partial sums of squares.
+constexpr int kMaxNormBatch = 16;
+struct NormEntry {
+  const void* g;
+  long long rows, cols, ldg;
+  __nv_bfloat16* xd;
+  long long ldxd;
+  __nv_bfloat16* xt;
+  long long ldxt;
+  float* partials;
+};
+struct NormTable {
+  NormEntry e[kMaxNormBatch];
+};
+
+// Blocks (= partial sums) of the sum-of-squares pass over n elements.  The fused momentum kernel
+// uses the same grid and the same element-to-thread assignment, so both produce the same
+// partial sums bit for bit.
+__host__ __device__ inline int norm_blocks(long long n) {
+  long long nb = (n + 8191) / 8192;
+  if (nb > kNormBlocks) nb = kNormBlocks;
+  if (nb < 1) nb = 1;
+  return (int)nb;
+}
+
 // ---------------------------------------------------------------- sum of squares, partials
 template <typename T>
 __global__ void __launch_bounds__(256)
-sumsq_partial_kernel(const T* __restrict__ g, long long rows, long long cols, long long ldg,
-                     int vec_ok, float* __restrict__ partials) {
+sumsq_partial_kernel(const __grid_constant__ NormTable tab, int vec_ok) {
   __shared__ float red[8];
   constexpr int V = 16 / sizeof(T);
+  const NormEntry& en = tab.e[blockIdx.y];
+  const T* __restrict__ g = reinterpret_cast<const T*>(en.g);
+  const long long rows = en.rows, cols = en.cols, ldg = en.ldg;
+  float* __restrict__ partials = en.partials;
   float s = 0.f;
   const long long n = rows * cols;
   if (vec_ok) {  // contiguous, 16-byte aligned, n % V == 0
@@ -80,12 +115,17 @@ sumsq_partial_kernel(const T* __restrict__ g, long long rows, long long cols, lo
 // all blocks derive the same denominator without a third launch.
 template <typename T>
 __global__ void __launch_bounds__(256)
-scale_transpose_kernel(const T* __restrict__ g, long long rows, long long cols, long long ldg,
-                       const float* __restrict__ partials, int nparts,
-                       __nv_bfloat16* __restrict__ xd, long long ldxd,
-                       __nv_bfloat16* __restrict__ xt, long long ldxt) {
+scale_transpose_kernel(const __grid_constant__ NormTable tab, int nparts) {
   __shared__ float red[8];
   __shared__ __nv_bfloat16 tile[64][66];
+  ptx_grid_dep_launch();  // the GEMM that follows may set itself up while this kernel runs
+  const NormEntry& en = tab.e[blockIdx.y];
+  const T* __restrict__ g = reinterpret_cast<const T*>(en.g);
+  const long long rows = en.rows, cols = en.cols, ldg = en.ldg;
+  const float* __restrict__ partials = en.partials;
+  __nv_bfloat16* __restrict__ xd = en.xd;
+  __nv_bfloat16* __restrict__ xt = en.xt;
+  const long long ldxd = en.ldxd, ldxt = en.ldxt;
   float s = 0.f;
   for (int i = threadIdx.x; i < nparts; i += 256) s += partials[i];
   const float total = block_sum_256(s, red);
@@ -131,10 +171,15 @@ scale_transpose_kernel(const T* __restrict__ g, long long rows, long long cols, 
 // outputs are written as whole 128-byte row segments.
 template <typename T>
 __global__ void __launch_bounds__(256)
-scale_transpose_vec_kernel(const T* __restrict__ g, long long rows, long long cols, long long ldg,
-                           const float* __restrict__ partials, int nparts,
-                           __nv_bfloat16* __restrict__ xd, long long ldxd,
-                           __nv_bfloat16* __restrict__ xt, long long ldxt) {
+scale_transpose_vec_kernel(const __grid_constant__ NormTable tab, int nparts) {
+  ptx_grid_dep_launch();
+  const NormEntry& en = tab.e[blockIdx.y];
+  const T* __restrict__ g = reinterpret_cast<const T*>(en.g);
+  const long long cols = en.cols, ldg = en.ldg;
+  const float* __restrict__ partials = en.partials;
+  __nv_bfloat16* __restrict__ xd = en.xd;
+  __nv_bfloat16* __restrict__ xt = en.xt;
+  const long long ldxd = en.ldxd, ldxt = en.ldxt;
   constexpr int V = 16 / sizeof(T);        // input elements per 16-byte load
   constexpr int CHUNKS = 64 / V;           // loads per tile row
   __shared__ float red[8];
@@ -194,16 +239,37 @@ __device__ __forceinline__ float lerp_f(float a, float b, float w) {
   return (fabsf(w) < 0.5f) ? a + w * (b - a) : b - (b - a) * (1.f - w);
 }
 
-template <typename T>
+// Tensors of one momentum launch (blockIdx.y selects one).  With `partials` the kernel also
+// leaves the partial sums of squares of the values Newton-Schulz will read (the gradient after
+// the Nesterov step, or the momentum buffer), saving the normalisation its own pass over them.
+constexpr int kMaxMomentumBatch = 16;
+struct MomentumTable {
+  void* grad[kMaxMomentumBatch];
+  void* buf[kMaxMomentumBatch];
+  float* partials[kMaxMomentumBatch];
+  long long n[kMaxMomentumBatch];
+};
+
+// kSumsq: the grid is norm_blocks(n) blocks and every thread walks the 16-byte vectors exactly
+// as sumsq_partial_kernel does (same stride, same order of the fused multiply-adds, same block
+// reduction), so partials[blockIdx.x] is bit for bit what that kernel would compute afterwards.
+// Requires 16-byte aligned tensors with n a multiple of the vector width.
+template <typename T, bool kSumsq>
 __global__ void __launch_bounds__(256)
-momentum_kernel(T* __restrict__ grad, T* __restrict__ buf, long long n, float w_buf, float w_grad,
-                int nesterov, int vec_ok) {
+momentum_kernel(const __grid_constant__ MomentumTable tab, float w_buf, float w_grad, int nesterov,
+                int vec_ok) {
   constexpr int V = 16 / sizeof(T);
+  __shared__ float red[8];
+  T* __restrict__ grad = reinterpret_cast<T*>(tab.grad[blockIdx.y]);
+  T* __restrict__ buf = reinterpret_cast<T*>(tab.buf[blockIdx.y]);
+  const long long n = tab.n[blockIdx.y];
   const long long stride = (long long)gridDim.x * 256;
+  float s = 0.f;
   if (vec_ok) {
     const long long nv = n / V;
     uint4* g4 = reinterpret_cast<uint4*>(grad);
     uint4* b4 = reinterpret_cast<uint4*>(buf);
+#pragma unroll 4
     for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < nv; i += stride) {
       uint4 graw = g4[i], braw = b4[i];
       T* ge = reinterpret_cast<T*>(&graw);
@@ -214,6 +280,10 @@ momentum_kernel(T* __restrict__ grad, T* __restrict__ buf, long long n, float w_
         const T nb = st_f<T>(lerp_f(ld_f<T>(be[j]), gv, w_buf));
         be[j] = nb;
         if (nesterov) ge[j] = st_f<T>(lerp_f(gv, ld_f<T>(nb), w_grad));
+        if (kSumsq) {
+          const float f = as_bf16_value<T>(nesterov ? ge[j] : nb);
+          s = fmaf(f, f, s);
+        }
       }
       b4[i] = braw;
       if (nesterov) g4[i] = graw;
@@ -232,6 +302,10 @@ momentum_kernel(T* __restrict__ grad, T* __restrict__ buf, long long n, float w_
       buf[i] = nb;
       if (nesterov) grad[i] = st_f<T>(lerp_f(gv, ld_f<T>(nb), w_grad));
     }
+  }
+  if (kSumsq) {
+    const float tot = block_sum_256(s, red);
+    if (threadIdx.x == 0) tab.partials[blockIdx.y][blockIdx.x] = tot;
   }
 }
 
@@ -300,34 +374,170 @@ int elementwise_grid(long long n, int per_thread) {
 }
 
 template <typename T>
-int normalize_t(const T* g, long long rows, long long cols, long long ldg, __nv_bfloat16* xd,
-                long long ldxd, __nv_bfloat16* xt, long long ldxt, float* partials,
-                cudaStream_t stream) {
-  const long long n = rows * cols;
+bool sumsq_vec_ok(const void* g, long long rows, long long cols, long long ldg) {
   constexpr int V = 16 / sizeof(T);
-  const int vec_ok = (ldg == cols) && ((reinterpret_cast<uintptr_t>(g) & 15u) == 0) && (n % V == 0);
-  long long nb = (n + 8191) / 8192;
-  if (nb > kNormBlocks) nb = kNormBlocks;
-  if (nb < 1) nb = 1;
-  sumsq_partial_kernel<T><<<(int)nb, 256, 0, stream>>>(g, rows, cols, ldg, vec_ok, partials);
-  FM_CUDA_CHECK(cudaGetLastError());
-  const long long tiles = ((rows + 63) / 64) * ((cols + 63) / 64);
-  if (tiles > 0x7fffffffLL) return fail(FM_ERR_UNSUPPORTED, "matrix too large");
-  const bool fast = (rows % 64 == 0) && (cols % 64 == 0) && (ldg % V == 0) &&
-                    ((reinterpret_cast<uintptr_t>(g) & 15u) == 0) &&
-                    (xd == nullptr || (ldxd % 8 == 0 && (reinterpret_cast<uintptr_t>(xd) & 15u) == 0)) &&
-                    (xt == nullptr || (ldxt % 8 == 0 && (reinterpret_cast<uintptr_t>(xt) & 15u) == 0));
-  if (fast)
-    scale_transpose_vec_kernel<T><<<(int)tiles, 256, 0, stream>>>(g, rows, cols, ldg, partials,
-                                                                  (int)nb, xd, ldxd, xt, ldxt);
-  else
-    scale_transpose_kernel<T><<<(int)tiles, 256, 0, stream>>>(g, rows, cols, ldg, partials, (int)nb,
-                                                              xd, ldxd, xt, ldxt);
+  return (ldg == cols || rows == 1) && ((reinterpret_cast<uintptr_t>(g) & 15u) == 0) &&
+         ((rows * cols) % V == 0);
+}
+
+// Partial sums of squares of `count` matrices of identical extents, one launch.
+template <typename T>
+int sumsq_batch_t(const NormTable& tab, int count, cudaStream_t stream) {
+  const NormEntry& e0 = tab.e[0];
+  int vec_ok = 1;
+  for (int i = 0; i < count; ++i)
+    vec_ok = vec_ok && sumsq_vec_ok<T>(tab.e[i].g, tab.e[i].rows, tab.e[i].cols, tab.e[i].ldg);
+  const dim3 grid((unsigned)norm_blocks(e0.rows * e0.cols), (unsigned)count);
+  sumsq_partial_kernel<T><<<grid, 256, 0, stream>>>(tab, vec_ok);
   FM_CUDA_CHECK(cudaGetLastError());
   return FM_OK;
 }
 
+template <typename T>
+int normalize_batch_t(const NormTable& tab, int count, bool sumsq_ready, cudaStream_t stream) {
+  constexpr int V = 16 / sizeof(T);
+  const NormEntry& e0 = tab.e[0];
+  const long long rows = e0.rows, cols = e0.cols;
+  if (!sumsq_ready) {
+    const int rc = sumsq_batch_t<T>(tab, count, stream);
+    if (rc != FM_OK) return rc;
+  }
+  const long long tiles = ((rows + 63) / 64) * ((cols + 63) / 64);
+  if (tiles > 0x7fffffffLL) return fail(FM_ERR_UNSUPPORTED, "matrix too large");
+  bool fast = (rows % 64 == 0) && (cols % 64 == 0);
+  for (int i = 0; i < count && fast; ++i) {
+    const NormEntry& e = tab.e[i];
+    fast = (e.ldg % V == 0) && ((reinterpret_cast<uintptr_t>(e.g) & 15u) == 0) &&
+           (e.xd == nullptr || (e.ldxd % 8 == 0 && (reinterpret_cast<uintptr_t>(e.xd) & 15u) == 0)) &&
+           (e.xt == nullptr || (e.ldxt % 8 == 0 && (reinterpret_cast<uintptr_t>(e.xt) & 15u) == 0));
+  }
+  const dim3 grid((unsigned)tiles, (unsigned)count);
+  const int nparts = norm_blocks(rows * cols);
+  if (fast)
+    scale_transpose_vec_kernel<T><<<grid, 256, 0, stream>>>(tab, nparts);
+  else
+    scale_transpose_kernel<T><<<grid, 256, 0, stream>>>(tab, nparts);
+  FM_CUDA_CHECK(cudaGetLastError());
+  return FM_OK;
+}
+
+int fill_norm_table(NormTable* tab, const NormItem* items, int count) {
+  if (count < 1 || count > kMaxNormBatch)
+    return fail(FM_ERR_INVALID, "normalisation batch must be 1..%d", kMaxNormBatch);
+  for (int i = 0; i < count; ++i) {
+    const NormItem& it = items[i];
+    if (!it.g || !it.partials || (!it.xd && !it.xt)) return fail(FM_ERR_INVALID, "null pointer");
+    if (it.rows != items[0].rows || it.cols != items[0].cols)
+      return fail(FM_ERR_INVALID, "matrices of a batch must have identical extents");
+    if (it.rows <= 0 || it.cols <= 0 || it.ldg < it.cols || (it.xd && it.ldxd < it.cols) ||
+        (it.xt && it.ldxt < it.rows))
+      return fail(FM_ERR_INVALID, "bad extents");
+    NormEntry& e = tab->e[i];
+    e.g = it.g; e.rows = it.rows; e.cols = it.cols; e.ldg = it.ldg;
+    e.xd = static_cast<__nv_bfloat16*>(it.xd); e.ldxd = it.ldxd;
+    e.xt = static_cast<__nv_bfloat16*>(it.xt); e.ldxt = it.ldxt;
+    e.partials = it.partials;
+  }
+  return FM_OK;
+}
+
+template <typename T>
+bool momentum_fusable_t(const MomentumItem* items, int count) {
+  constexpr int V = 16 / sizeof(T);
+  for (int i = 0; i < count; ++i) {
+    if ((reinterpret_cast<uintptr_t>(items[i].grad) & 15u) != 0 ||
+        (reinterpret_cast<uintptr_t>(items[i].buf) & 15u) != 0 || items[i].n % V != 0 ||
+        items[i].n != items[0].n)
+      return false;
+  }
+  return true;
+}
+
+template <typename T>
+int momentum_batch_t(const MomentumItem* items, int count, double momentum, int nesterov,
+                     cudaStream_t stream) {
+  MomentumTable tab;
+  long long nmax = 0;
+  bool want_sumsq = true;
+  int vec_ok = 1;
+  for (int i = 0; i < count; ++i) {
+    tab.grad[i] = items[i].grad;
+    tab.buf[i] = items[i].buf;
+    tab.partials[i] = items[i].partials;
+    tab.n[i] = items[i].n;
+    if (items[i].n > nmax) nmax = items[i].n;
+    if (!items[i].partials) want_sumsq = false;
+    vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(items[i].grad) & 15u) == 0) &&
+             ((reinterpret_cast<uintptr_t>(items[i].buf) & 15u) == 0);
+  }
+  if (nmax == 0) return FM_OK;
+  // the reference passes python floats: lerp_(g, 1 - momentum) and lerp_(buf, momentum)
+  const float w_buf = (float)(1.0 - momentum);
+  const float w_grad = (float)momentum;
+  if (want_sumsq && momentum_fusable_t<T>(items, count)) {
+    const dim3 grid((unsigned)norm_blocks(nmax), (unsigned)count);
+    momentum_kernel<T, true><<<grid, 256, 0, stream>>>(tab, w_buf, w_grad, nesterov, 1);
+    FM_CUDA_CHECK(cudaGetLastError());
+    return FM_OK;
+  }
+  int gx = elementwise_grid(nmax, sizeof(T) == 4 ? 4 : 8);
+  gx = (gx + count - 1) / count;  // share the SMs between the tensors of the launch
+  const dim3 grid((unsigned)(gx < 1 ? 1 : gx), (unsigned)count);
+  momentum_kernel<T, false><<<grid, 256, 0, stream>>>(tab, w_buf, w_grad, nesterov, vec_ok);
+  FM_CUDA_CHECK(cudaGetLastError());
+  if (!want_sumsq) return FM_OK;
+  // tensors the fused kernel cannot take (odd sizes or alignment): a separate pass over the
+  // values Newton-Schulz will read leaves the same partial sums
+  for (int i = 0; i < count; ++i) {
+    if (items[i].n == 0) continue;
+    NormTable nt;
+    NormEntry& e = nt.e[0];
+    e.g = nesterov ? items[i].grad : items[i].buf;
+    e.rows = 1; e.cols = items[i].n; e.ldg = items[i].n;
+    e.xd = nullptr; e.ldxd = 0; e.xt = nullptr; e.ldxt = 0;
+    e.partials = items[i].partials;
+    const int rc = sumsq_batch_t<T>(nt, 1, stream);
+    if (rc != FM_OK) return rc;
+  }
+  return FM_OK;
+}
+
 }  // namespace
+
+int normalize_batch(const NormItem* items, int count, int g_dtype, bool sumsq_ready,
+                    cudaStream_t stream) {
+  NormTable tab;
+  const int rc = fill_norm_table(&tab, items, count);
+  if (rc != FM_OK) return rc;
+  switch (g_dtype) {
+    case FM_BF16: return normalize_batch_t<__nv_bfloat16>(tab, count, sumsq_ready, stream);
+    case FM_F16: return normalize_batch_t<__half>(tab, count, sumsq_ready, stream);
+    case FM_F32: return normalize_batch_t<float>(tab, count, sumsq_ready, stream);
+    default: return fail(FM_ERR_UNSUPPORTED, "unknown dtype %d", g_dtype);
+  }
+}
+
+int momentum_batch(const MomentumItem* items, int count, int dtype, double momentum, int nesterov,
+                   cudaStream_t stream) {
+  if (count < 0) return fail(FM_ERR_INVALID, "negative tensor count");
+  for (int base = 0; base < count; base += kMaxMomentumBatch) {
+    const int m = (count - base) < kMaxMomentumBatch ? (count - base) : kMaxMomentumBatch;
+    for (int i = 0; i < m; ++i) {
+      if (!items[base + i].grad || !items[base + i].buf) return fail(FM_ERR_INVALID, "null pointer");
+      if (items[base + i].n < 0) return fail(FM_ERR_INVALID, "negative element count");
+    }
+    int rc;
+    switch (dtype) {
+      case FM_BF16: rc = momentum_batch_t<__nv_bfloat16>(items + base, m, momentum, nesterov, stream); break;
+      case FM_F16: rc = momentum_batch_t<__half>(items + base, m, momentum, nesterov, stream); break;
+      case FM_F32: rc = momentum_batch_t<float>(items + base, m, momentum, nesterov, stream); break;
+      default: return fail(FM_ERR_UNSUPPORTED, "unknown dtype %d", dtype);
+    }
+    if (rc != FM_OK) return rc;
+  }
+  return FM_OK;
+}
+
 }  // namespace fm
 
 extern "C" size_t fm_norm_scratch_floats(void) { return fm::kNormBlocks; }
@@ -337,58 +547,20 @@ extern "C" int fm_normalize(const void* G, int64_t rows, int64_t cols, int64_t l
                             void* stream) {
   using namespace fm;
   clear_error();
-  if (!G || !partials || (!xd && !xt)) return fail(FM_ERR_INVALID, "null pointer");
-  if (rows <= 0 || cols <= 0 || ldg < cols || (xd && ldxd < cols) || (xt && ldxt < rows))
-    return fail(FM_ERR_INVALID, "bad extents");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  switch (g_dtype) {
-    case FM_BF16:
-      return normalize_t<__nv_bfloat16>((const __nv_bfloat16*)G, rows, cols, ldg,
-                                        (__nv_bfloat16*)xd, ldxd, (__nv_bfloat16*)xt, ldxt,
-                                        partials, st);
-    case FM_F16:
-      return normalize_t<__half>((const __half*)G, rows, cols, ldg, (__nv_bfloat16*)xd, ldxd,
-                                 (__nv_bfloat16*)xt, ldxt, partials, st);
-    case FM_F32:
-      return normalize_t<float>((const float*)G, rows, cols, ldg, (__nv_bfloat16*)xd, ldxd,
-                                (__nv_bfloat16*)xt, ldxt, partials, st);
-    default:
-      return fail(FM_ERR_UNSUPPORTED, "unknown dtype %d", g_dtype);
-  }
+  NormItem it;
+  it.g = G; it.rows = rows; it.cols = cols; it.ldg = ldg;
+  it.xd = xd; it.ldxd = ldxd; it.xt = xt; it.ldxt = ldxt;
+  it.partials = partials;
+  return normalize_batch(&it, 1, g_dtype, false, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int fm_momentum(void* grad, void* buf, int64_t n, int dtype, double momentum,
-                           int nesterov, void* stream) {
+                           int nesterov, float* sumsq_partials, void* stream) {
   using namespace fm;
   clear_error();
-  if (!grad || !buf) return fail(FM_ERR_INVALID, "null pointer");
-  if (n < 0) return fail(FM_ERR_INVALID, "negative element count");
-  if (n == 0) return FM_OK;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // the reference passes python floats: lerp_(g, 1 - momentum) and lerp_(buf, momentum)
-  const float w_buf = (float)(1.0 - momentum);
-  const float w_grad = (float)momentum;
-  const int vec_ok = ((reinterpret_cast<uintptr_t>(grad) & 15u) == 0) &&
-                     ((reinterpret_cast<uintptr_t>(buf) & 15u) == 0);
-  const int grid = elementwise_grid(n, dtype == FM_F32 ? 4 : 8);
-  switch (dtype) {
-    case FM_BF16:
-      momentum_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16*)grad, (__nv_bfloat16*)buf,
-                                                           n, w_buf, w_grad, nesterov, vec_ok);
-      break;
-    case FM_F16:
-      momentum_kernel<__half><<<grid, 256, 0, st>>>((__half*)grad, (__half*)buf, n, w_buf, w_grad,
-                                                    nesterov, vec_ok);
-      break;
-    case FM_F32:
-      momentum_kernel<float><<<grid, 256, 0, st>>>((float*)grad, (float*)buf, n, w_buf, w_grad,
-                                                   nesterov, vec_ok);
-      break;
-    default:
-      return fail(FM_ERR_UNSUPPORTED, "unknown dtype %d", dtype);
-  }
-  FM_CUDA_CHECK(cudaGetLastError());
-  return FM_OK;
+  MomentumItem it;
+  it.grad = grad; it.buf = buf; it.n = n; it.partials = sumsq_partials;
+  return momentum_batch(&it, 1, dtype, momentum, nesterov, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int fm_update_multi(void* const* params, const void* const* updates,

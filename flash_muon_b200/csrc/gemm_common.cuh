@@ -8,6 +8,8 @@
 
 namespace fm {
 
+constexpr int kMaxGemmBatch = 16;
+
 struct GemmParams {
   int M, N, K;
   int sym;        // 1: triangular schedule + mirrored store (requires A == B, M == N)
@@ -34,23 +36,37 @@ struct GemmParams {
   float* sk_ws;            // scratch for partial accumulators
   unsigned int* sk_cnt;    // per (tile, CTA rank) count of deposited parts, zero between launches
   unsigned int* err;
-#ifdef FM_TRACE
-  unsigned long long* trace;  // diagnostic builds only: 8 timestamps per CTA
-#endif
+  // Batched launch (CTA-pair kernel): `batch` problems of identical extents whose operands are
+  // stacked along the rows of one tensor map each; the tile list is the single-problem list
+  // repeated `batch` times.  batch == 1: plain launch, every field below is zero.
+  int batch;
+  int tiles_per_batch;
+  int a_batch_rows, b_batch_rows;       // rows between consecutive problems in the operand stacks
+  long long d_batch, c_batch, t_batch;  // elements between consecutive problems in D, C, CT
+  int use_c_tab;                        // 1: problem g writes its direct output to c_tab[g]
+  void* c_tab[kMaxGemmBatch];
 };
 
-#ifdef FM_TRACE
-__device__ __forceinline__ void trace_mark(const GemmParams& p, int slot) {
-  if (p.trace != nullptr) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    p.trace[(size_t)blockIdx.x * 8 + slot] = t;
+// Base pointers of one problem of a (possibly batched) launch.
+struct EpiPtrs {
+  const void* D;
+  void* C;
+  void* CT;
+};
+
+__device__ __forceinline__ EpiPtrs epilogue_ptrs(const GemmParams& p, int g, int elem_bytes) {
+  EpiPtrs e;
+  e.D = p.D;
+  e.C = p.C;
+  e.CT = p.CT;
+  if (p.batch > 1) {
+    if (e.D) e.D = static_cast<const char*>(p.D) + (long long)g * p.d_batch * elem_bytes;
+    if (p.use_c_tab) e.C = p.c_tab[g];
+    else if (e.C) e.C = static_cast<char*>(p.C) + (long long)g * p.c_batch * elem_bytes;
+    if (e.CT) e.CT = static_cast<char*>(p.CT) + (long long)g * p.t_batch * elem_bytes;
   }
+  return e;
 }
-#define FM_TRACE_MARK(p, slot) ::fm::trace_mark(p, slot)
-#else
-#define FM_TRACE_MARK(p, slot) ((void)0)
-#endif
 
 template <typename T>
 struct Num;
@@ -69,8 +85,9 @@ struct Num<__half> {
 
 // Addend values D[row][c0 .. c0+31] of one epilogue chunk (zeros outside the matrix).
 template <typename T>
-__device__ __forceinline__ void epilogue_load_d(const GemmParams& p, int row, int c0, T (&dv)[32]) {
-  const T* Dp = reinterpret_cast<const T*>(p.D);
+__device__ __forceinline__ void epilogue_load_d(const GemmParams& p, const EpiPtrs& e, int row, int c0,
+                                                T (&dv)[32]) {
+  const T* Dp = reinterpret_cast<const T*>(e.D);
   if (Dp == nullptr) return;
   if (row < p.M && c0 < p.N) {
     const T* dptr = Dp + (long long)row * p.ldd + c0;
@@ -95,8 +112,9 @@ __device__ __forceinline__ void epilogue_load_d(const GemmParams& p, int row, in
 // produced by the block above the diagonal); on the diagonal only c >= row is stored and
 // c > row mirrored, so both triangles come from the same rounded registers.
 template <typename T>
-__device__ __forceinline__ void epilogue_store(const GemmParams& p, const uint32_t (&raw)[32],
-                                               const T (&dv)[32], int row, int c0, int bi) {
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiPtrs& e,
+                                               const uint32_t (&raw)[32], const T (&dv)[32], int row,
+                                               int c0, int bi) {
   if (c0 >= p.N) return;  // warp-uniform
   const int cb = c0 >> 7;
   if (p.sym && cb < bi) return;  // warp-uniform
@@ -111,11 +129,11 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const uint32
   }
   const bool full_cols = (c0 + 32 <= p.N);
   const bool row_ok = row < p.M;
-  T* const Cp = reinterpret_cast<T*>(p.C);
-  T* const CTp = reinterpret_cast<T*>(p.CT);
+  T* const Cp = reinterpret_cast<T*>(e.C);
+  T* const CTp = reinterpret_cast<T*>(e.CT);
 
   alignas(16) T outv[32];
-  if (p.D != nullptr) {
+  if (e.D != nullptr) {
     if (p.precise) {
 #pragma unroll
       for (int j = 0; j < 32; ++j)

@@ -17,8 +17,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include <cstdlib>
-
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "gemm_tc.cuh"
@@ -47,7 +45,7 @@ struct Cfg {
 template <typename T, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const GemmParams p) {
+               const __grid_constant__ GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -66,7 +64,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) FM_TRACE_MARK(p, 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -90,7 +87,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) FM_TRACE_MARK(p, 1);
+  // Nothing above touches global memory: with programmatic stream serialization the set-up runs
+  // while the previous kernel of the stream drains; from here on its results are visible.
+  ptx::grid_dep_wait();
+  const EpiPtrs ep = epilogue_ptrs(p, 0, (int)sizeof(T));
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
@@ -98,7 +98,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      if ((int)blockIdx.x >= p.num_tiles) ptx::grid_dep_launch();
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+        if (t + (int)gridDim.x >= p.num_tiles) ptx::grid_dep_launch();  // this CTA's last tile
         const Tile tl = decode_tile<BN>(p, t);
         const int nb = tl.ncols >> 7;
         for (int kb = 0; kb < p.num_kb; ++kb) {
@@ -108,7 +110,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int q = 0; q < nb; ++q)
             ptx::tma_load_2d(b_smem(s) + q * kSlabBytes, &tmB, full_bar(s), kb * BK,
                              tl.n0 + q * 128);
-          if (t == (int)blockIdx.x && kb == 0) FM_TRACE_MARK(p, 2);
           if (++s == C::kStages) { s = 0; ph ^= 1u; }
         }
       }
@@ -130,7 +131,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t idesc = ptx::make_idesc_f16(Num<T>::kFormat, BM, (uint32_t)tl.ncols);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
-          if (kb == 0) FM_TRACE_MARK(p, 3);
           ptx::tc_fence_after();
           const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_smem(s));
           const uint64_t b_desc = ptx::make_kmajor_sw128_desc(b_smem(s));
@@ -145,7 +145,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (++s == C::kStages) { s = 0; ph ^= 1u; }
         }
         if (!ok) break;
-        FM_TRACE_MARK(p, 4);
         ptx::umma_commit(tfull_bar(acc));  // accumulator complete
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
@@ -163,26 +162,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int nchunks = tl.ncols >> 5;
       // the addend does not depend on the accumulator: fetch the first chunk before waiting
       alignas(16) T dcur[32], dnext[32];
-      epilogue_load_d<T>(p, row, tl.n0, dcur);
+      epilogue_load_d<T>(p, ep, row, tl.n0, dcur);
       bool ok = ptx::mbar_wait(tfull_bar(acc), acc_ph, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (threadIdx.x == 64) FM_TRACE_MARK(p, 5);
       ptx::tc_fence_after();
       for (int ch = 0; ch < nchunks; ++ch) {
         uint32_t raw[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + ch * 32),
                            raw);
-        if (ch + 1 < nchunks) epilogue_load_d<T>(p, row, tl.n0 + (ch + 1) * 32, dnext);
+        if (ch + 1 < nchunks) epilogue_load_d<T>(p, ep, row, tl.n0 + (ch + 1) * 32, dnext);
         ptx::tmem_ld_wait();
-        epilogue_store<T>(p, raw, dcur, row, tl.n0 + ch * 32, tl.bi);
+        epilogue_store<T>(p, ep, raw, dcur, row, tl.n0 + ch * 32, tl.bi);
         if (p.D != nullptr) {
 #pragma unroll
           for (int v = 0; v < 4; ++v)
             reinterpret_cast<uint4*>(dcur)[v] = reinterpret_cast<const uint4*>(dnext)[v];
         }
       }
-      if (threadIdx.x == 64) FM_TRACE_MARK(p, 6);
       ptx::tc_fence_before();
       ptx::mbar_arrive(tempty_bar(acc));
       acc ^= 1;
@@ -202,7 +199,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   }
-  if (threadIdx.x == 0) FM_TRACE_MARK(p, 7);
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 0x47450000u | (unsigned)blockIdx.x);
 }
 
@@ -221,17 +217,21 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaSt
   const int sms = sm_count();
   if (sms <= 0) return fail(FM_ERR_CUDA, "could not query the SM count");
   const int grid = p.num_tiles < sms ? p.num_tiles : sms;
-  gemm_tc_kernel<T, BN><<<grid, kThreads, C::kSmemBytes, stream>>>(tmA, tmB, p);
-  FM_CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = options().pdl ? 1 : 0;
+  FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<T, BN>, tmA, tmB, p));
   return FM_OK;
 }
 
 }  // namespace
-
-#ifdef FM_TRACE
-static unsigned long long* g_trace_ptr = nullptr;
-extern "C" void fm_debug_set_trace(void* ptr) { g_trace_ptr = static_cast<unsigned long long*>(ptr); }
-#endif
 
 int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   if (a.dtype != FM_BF16 && a.dtype != FM_F16)
@@ -241,11 +241,19 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
                 (long long)a.N, (long long)a.K);
   if (!a.A || !a.B || (!a.C && !a.CT)) return fail(FM_ERR_INVALID, "null operand or no output");
   if (a.sym && (a.M != a.N)) return fail(FM_ERR_INVALID, "symmetric mode needs M == N");
+  if (a.batch < 1 || a.batch > kMaxGemmBatch)
+    return fail(FM_ERR_INVALID, "batch must be 1..%d, got %d", kMaxGemmBatch, a.batch);
+  if (a.batch > 1 && (a.a_batch_rows < a.M || a.b_batch_rows < a.N))
+    return fail(FM_ERR_INVALID, "stacked operands overlap: batch rows smaller than the extents");
 
+  // operands of a batch are stacked along the rows: one tensor map covers all of them, rows
+  // past the last problem read as zeros
+  const uint64_t rows_a = (uint64_t)(a.batch - 1) * (uint64_t)a.a_batch_rows + (uint64_t)a.M;
+  const uint64_t rows_b = (uint64_t)(a.batch - 1) * (uint64_t)a.b_batch_rows + (uint64_t)a.N;
   CUtensorMap tmA, tmB;
-  int rc = encode_tmap_2d(&tmA, a.dtype, a.A, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.lda, BK, 128);
+  int rc = encode_tmap_2d(&tmA, a.dtype, a.A, (uint64_t)a.K, rows_a, (uint64_t)a.lda, BK, 128);
   if (rc != FM_OK) return rc;
-  rc = encode_tmap_2d(&tmB, a.dtype, a.B, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.ldb, BK, 128);
+  rc = encode_tmap_2d(&tmB, a.dtype, a.B, (uint64_t)a.K, rows_b, (uint64_t)a.ldb, BK, 128);
   if (rc != FM_OK) return rc;
 
   GemmParams p;
@@ -267,32 +275,51 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   p.stages = 0;
   p.strip_w = 0;
   p.sk_dp_tiles = 0; p.sk_per = 0; p.sk_total = 0; p.sk_ws = nullptr; p.sk_cnt = nullptr;
+  p.batch = a.batch;
+  p.tiles_per_batch = 0;
+  p.a_batch_rows = (int)a.a_batch_rows; p.b_batch_rows = (int)a.b_batch_rows;
+  p.d_batch = a.d_batch; p.c_batch = a.c_batch; p.t_batch = a.t_batch;
+  p.use_c_tab = (a.batch > 1 && a.c_tab != nullptr) ? 1 : 0;
+  for (int g = 0; g < kMaxGemmBatch; ++g) p.c_tab[g] = (p.use_c_tab && g < a.batch) ? a.c_tab[g] : nullptr;
+  if (p.use_c_tab) {  // the fast store path must hold for every problem's output
+    p.c_vec = (a.ldc_c == 1) && (a.ldc_r % 8 == 0);
+    for (int g = 0; g < a.batch; ++g) {
+      if (!a.c_tab[g]) return fail(FM_ERR_INVALID, "null output pointer for problem %d", g);
+      if ((reinterpret_cast<uintptr_t>(a.c_tab[g]) & 15u) != 0) p.c_vec = 0;
+    }
+  } else if (a.batch > 1) {  // per-problem offsets must keep the alignment the fast paths assume
+    if (a.D && a.d_batch % 8 != 0) p.d_vec = 0;
+    if (a.C && a.c_batch % 8 != 0) p.c_vec = 0;
+    if (a.CT && a.t_batch % 2 != 0) p.t_pack = 0;
+  }
+  if (a.batch > 1 && p.use_c_tab && a.D && a.d_batch % 8 != 0) p.d_vec = 0;
+  if (a.batch > 1 && p.use_c_tab && a.CT && a.t_batch % 2 != 0) p.t_pack = 0;
   p.err = device_error_word();
-#ifdef FM_TRACE
-  p.trace = g_trace_ptr;
-#endif
   if (!p.err) return fail(FM_ERR_CUDA, "no current CUDA device");
 
   // CTA pairs on 256 x 256 tiles when there are enough tiles to occupy most of the pairs;
   // otherwise single CTAs on 128 x 256 or 128 x 128 tiles (more, smaller units of work).
+  // A batch always runs on pairs (the single-CTA kernel has no batch dimension).
   int impl = 1;
   {
-    const int tiles2 = gemm_tc2_tiles(a.M, a.N, a.sym);
+    const int tiles2 = gemm_tc2_tiles(a.M, a.N, a.sym) * a.batch;
     const int pairs = gemm_tc2_max_pairs(a.dtype);
     if (pairs > 0 && tiles2 * 10 >= pairs * 6) impl = 2;
-    if (const char* e = getenv("FM_GEMM_IMPL")) {
-      const int v = atoi(e);
-      if (v == 1 || (v == 2 && pairs > 0)) impl = v;
+    const int v = options().gemm_impl;
+    if (v == 1 || (v == 2 && pairs > 0)) impl = v;
+    if (a.batch > 1) {
+      if (pairs <= 0) return fail(FM_ERR_CUDA, "no resident CTA pair possible for a batched GEMM");
+      impl = 2;
     }
   }
-  if (impl == 2) return gemm_tc2_launch(a.dtype, tmA, tmB, p, stream);
+  if (impl == 2) return gemm_tc2_launch(a.dtype, tmA, tmB, p, a.sk_ws, a.sk_bytes, stream);
 
   // Tile width: 256 columns (less operand traffic per FLOP) unless that leaves most SMs idle.
   int bn = 256;
   const int sms = sm_count();
   if (count_tiles<256>(p.M, p.N, p.sym) < sms) bn = 128;
-  if (const char* e = getenv("FM_GEMM_BN")) {
-    const int v = atoi(e);
+  {
+    const int v = options().gemm_bn;
     if (v == 128 || v == 256) bn = v;
   }
   if (a.dtype == FM_BF16)
@@ -300,6 +327,12 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
                      : launch<__nv_bfloat16, 128>(tmA, tmB, p, stream);
   return bn == 256 ? launch<__half, 256>(tmA, tmB, p, stream)
                    : launch<__half, 128>(tmA, tmB, p, stream);
+}
+
+size_t gemm_sk_bytes(int dtype, int64_t M, int64_t N, int64_t K, int sym) {
+  if (dtype != FM_BF16 && dtype != FM_F16) return 0;
+  if (options().gemm_impl == 1) return 0;
+  return gemm_tc2_sk_bytes(dtype, M, N, K, sym);
 }
 
 }  // namespace fm

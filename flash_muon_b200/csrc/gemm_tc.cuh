@@ -22,7 +22,25 @@ struct GemmArgs {
   int64_t ldc_r = 0, ldc_c = 1;
   void* CT = nullptr;        // element (r,c) at CT[c*ldt_r + r*ldt_c]
   int64_t ldt_r = 0, ldt_c = 1;
+  // Batched launch: `batch` problems of identical extents.  Problem g reads rows
+  // [g*a_batch_rows, +M) of A and [g*b_batch_rows, +N) of B (the operands of all problems are
+  // stacked along the rows of one allocation each) and addresses D, C, CT at g*{d,c,t}_batch
+  // elements from their bases; with c_tab (host array of `batch` pointers) the direct output of
+  // problem g goes to c_tab[g] instead.
+  int batch = 1;
+  int64_t a_batch_rows = 0, b_batch_rows = 0;
+  int64_t d_batch = 0, c_batch = 0, t_batch = 0;
+  void* const* c_tab = nullptr;
+  // Scratch for the balanced tail of long tile lists (may be null: tiles are then dealt whole).
+  // gemm_sk_bytes() bytes, 256-byte aligned, owned by the caller; launches that may overlap on
+  // the GPU need distinct scratch.
+  void* sk_ws = nullptr;
+  size_t sk_bytes = 0;
 };
+
+// Bytes of scratch with which a product of these extents runs the balanced tail (0: it never
+// would, whatever scratch is offered).
+size_t gemm_sk_bytes(int dtype, int64_t M, int64_t N, int64_t K, int sym);
 
 // Validates, encodes the tensor maps and enqueues the kernel on `stream`.
 int gemm_tc(const GemmArgs& args, cudaStream_t stream);
@@ -32,7 +50,8 @@ struct GemmParams;
 int gemm_tc2_tiles(int64_t M, int64_t N, int sym);
 int gemm_tc2_max_pairs(int dtype);
 int gemm_tc2_launch(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
-                    cudaStream_t stream);
+                    void* sk_ws, size_t sk_bytes, cudaStream_t stream);
+size_t gemm_tc2_sk_bytes(int dtype, int64_t M, int64_t N, int64_t K, int sym);
 
 // Exact-fp32 FFMA symmetric rank-k update for f32 inputs and layouts TMA cannot address.
 int syrk_simt(const void* x, void* y, int64_t M, int64_t K, int64_t ldx, int64_t ldy_row,

@@ -10,11 +10,17 @@
 // Roles per CTA (192 threads): warp 0 TMA producer (both CTAs), warp 1 MMA issuer (leader CTA
 // only; both CTAs take part in the TMEM allocation), warps 2..5 epilogue (both CTAs, each for
 // its own 128 accumulator rows).
+//
+// A launch may carry a batch of problems of identical extents (operands stacked along the rows
+// of one tensor map each): the tile list is then the single-problem list repeated per problem,
+// so that many small matrices share one launch -- the grouped form Newton-Schulz uses for
+// matrices too small to fill the GPU on their own.
+//
+// The kernel is launched with programmatic stream serialization: its set-up (barriers, TMEM,
+// tensor-map prefetch) runs while the previous kernel of the stream drains, and every CTA lets
+// the next kernel be scheduled when it starts its last piece of work.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
-
-#include <cstdlib>
-#include <mutex>
 
 #include "common.cuh"
 #include "gemm_common.cuh"
@@ -29,20 +35,42 @@ constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr int kSlabBytes = 128 * BK * 2;      // 16 KiB: 128 rows x 64 columns of 16-bit values
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 7;
+constexpr int kDefaultStages = 6;
 constexpr int kStageBytes = 2 * kSlabBytes;   // this CTA's A slab + B slab
 constexpr int kTmemCols = 512;                // two accumulators of 256 fp32 columns
 constexpr int kNumBars = 2 * kMaxStages + 4;
 constexpr int smem_bytes(int stages) { return stages * kStageBytes + kNumBars * 8 + 16 + 1024; }
 
+// Scratch of the balanced tail: deposit counters first, then one partial accumulator per CTA of
+// every pair (128 rows x 256 fp32 columns each: a pair leaves at most one tile unfinished).
+constexpr size_t kSkCntBytes = 4096;
+constexpr size_t kSkPartBytes = (size_t)128 * 256 * 4;
+
+// Problem and tile of entry `t` of a (possibly batched) tile list.
+struct TileRef {
+  int g;
+  Tile2 tl;
+};
+__device__ __forceinline__ TileRef locate(const GemmParams& p, int t) {
+  TileRef r;
+  r.g = 0;
+  if (p.batch > 1) {
+    r.g = t / p.tiles_per_batch;
+    t -= r.g * p.tiles_per_batch;
+  }
+  r.tl = decode_tile2(p, t);
+  return r;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const GemmParams p) {
+                const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  const int kStages = p.stages;  // ring depth chosen by the host (shared memory left to others)
+  const int kStages = p.stages;  // ring depth chosen by the host
   const uint32_t smem_base = ptx::smem_u32(smem);
   const uint32_t bar_base = smem_base + kStages * kStageBytes;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kStages * kStageBytes + kNumBars * 8);
@@ -57,7 +85,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) FM_TRACE_MARK(p, 0);
   const uint32_t rank = ptx::cluster_ctarank();  // 0 = leader (issues the MMAs)
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
@@ -85,7 +112,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   ptx::cluster_sync();  // the peer's barriers exist before anything remote touches them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) FM_TRACE_MARK(p, 1);
+  // Nothing above reads or writes global memory; everything below may depend on the previous
+  // kernel of the stream.
+  ptx::grid_dep_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer (both CTAs)
@@ -94,23 +123,29 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t ph = 0;
       bool ok = true;
       WorkIter it(p, pair, npairs);
-      WorkItem w;
-      bool first = true;
-      while (ok && it.next(p, w)) {
-        const Tile2 tl = decode_tile2(p, w.tile);
+      WorkItem w, nxt;
+      bool have = it.next(p, w);
+      if (!have) ptx::grid_dep_launch();
+      while (ok && have) {
+        const bool more = it.next(p, nxt);
+        if (!more) ptx::grid_dep_launch();  // last piece of work of this CTA: the next kernel may be placed
+        const TileRef tr = locate(p, w.tile);
+        const Tile2 tl = tr.tl;
+        const int ya = tr.g * p.a_batch_rows + tl.m0 + (int)rank * 128;
+        const int yb = tr.g * p.b_batch_rows + tl.n0 + (int)rank * 128;
+        // On a diagonal tile of the symmetric product the B slab is the A slab (same rows of
+        // the same matrix): load it once and let the MMA read it through both descriptors.
+        const bool same = p.sym && (tl.m0 == tl.n0);
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t leader_full = ptx::mapa(full_bar(s), 0);
-          // On a diagonal tile of the symmetric product the B slab is the A slab (same rows of
-          // the same matrix): load it once and let the MMA read it through both descriptors.
-          const bool same = p.sym && (tl.m0 == tl.n0);
           if (rank == 0) ptx::mbar_expect_tx(full_bar(s), (same ? 2u : 4u) * kSlabBytes);
-          ptx::tma_load_2d_pair(a_smem(s), &tmA, leader_full, kb * BK, tl.m0 + (int)rank * 128);
-          if (!same)
-            ptx::tma_load_2d_pair(b_smem(s), &tmB, leader_full, kb * BK, tl.n0 + (int)rank * 128);
-          if (first) { FM_TRACE_MARK(p, 2); first = false; }
+          ptx::tma_load_2d_pair(a_smem(s), &tmA, leader_full, kb * BK, ya);
+          if (!same) ptx::tma_load_2d_pair(b_smem(s), &tmB, leader_full, kb * BK, yb);
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
+        w = nxt;
+        have = more;
       }
     }
     __syncwarp();
@@ -129,11 +164,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (!ptx::mbar_wait_cluster(tempty_bar(acc), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
-        const Tile2 tl = decode_tile2(p, w.tile);
+        const Tile2 tl = locate(p, w.tile).tl;
         const bool same = p.sym && (tl.m0 == tl.n0);
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
-          if (kb == w.kb0) FM_TRACE_MARK(p, 3);
           ptx::tc_fence_after();
           const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_smem(s));
           const uint64_t b_desc = same ? a_desc : ptx::make_kmajor_sw128_desc(b_smem(s));
@@ -145,7 +179,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
         if (!ok) break;
-        FM_TRACE_MARK(p, 4);
         ptx::umma_commit_pair(tfull_bar(acc), 0x3);  // accumulator halves complete in both CTAs
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
@@ -161,12 +194,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     WorkIter it(p, pair, npairs);
     WorkItem w;
     while (it.next(p, w)) {
-      const Tile2 tl = decode_tile2(p, w.tile);
+      const TileRef tr = locate(p, w.tile);
+      const Tile2 tl = tr.tl;
+      const EpiPtrs ep = epilogue_ptrs(p, tr.g, (int)sizeof(T));
       const int row_local = q * 32 + lane;
       const int row = tl.m0 + (int)rank * 128 + row_local;
       const int bi = (tl.m0 >> 7) + (int)rank;
       alignas(16) T dcur[32], dnext[32];
-      if (!w.deposit) epilogue_load_d<T>(p, row, tl.n0, dcur);
+      if (!w.deposit) epilogue_load_d<T>(p, ep, row, tl.n0, dcur);
 
       // parts of this tile deposited by earlier pairs: pairs c_first .. pair-1
       int c_first = pair;
@@ -218,7 +253,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       bool ok = ptx::mbar_wait(tfull_bar(acc), acc_ph, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (threadIdx.x == 64) FM_TRACE_MARK(p, 5);
       ptx::tc_fence_after();
       const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 256);
       if (!w.deposit) {
@@ -227,7 +261,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           uint32_t raw[32];
           ptx::tmem_ld_32x32(t_acc + (uint32_t)(ch * 32), raw);
           if (ch + 1 < 8) {
-            epilogue_load_d<T>(p, row, tl.n0 + (ch + 1) * 32, dnext);
+            epilogue_load_d<T>(p, ep, row, tl.n0 + (ch + 1) * 32, dnext);
             if (w.gather) load_parts(ch + 1, pnext);
           }
           ptx::tmem_ld_wait();
@@ -235,8 +269,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
             for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(psum[j] + __uint_as_float(raw[j]));
           }
-          epilogue_store<T>(p, raw, dcur, row, tl.n0 + ch * 32, bi);
-          if (p.D != nullptr) {
+          epilogue_store<T>(p, ep, raw, dcur, row, tl.n0 + ch * 32, bi);
+          if (ep.D != nullptr) {
 #pragma unroll
             for (int v = 0; v < 4; ++v)
               reinterpret_cast<uint4*>(dcur)[v] = reinterpret_cast<const uint4*>(dnext)[v];
@@ -261,7 +295,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 make_uint4(raw[4 * v], raw[4 * v + 1], raw[4 * v + 2], raw[4 * v + 3]);
         }
       }
-      if (threadIdx.x == 64) FM_TRACE_MARK(p, 6);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0));
@@ -273,9 +306,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (threadIdx.x == 64) atomicAdd(p.sk_cnt + (w.sk_tile * 2 + (int)rank), 1u);
-      } else if (w.gather) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 64) *cnt = 0u;  // every deposit was consumed: ready for the next launch
       }
     }
   }
@@ -291,137 +321,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     ptx::tc_fence_after();
     ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
   }
-  if (threadIdx.x == 0) FM_TRACE_MARK(p, 7);
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 0x47320000u | (unsigned)blockIdx.x);
 }
 
-// Ring depth: 6 stages of 32 KiB; 4 cost 2-3 % on the large products, 3 cost 12 %.
+// Ring depth: 6 stages of 32 KiB by default; 4 cost 2-3 % on the large products, 3 cost 12 %.
 int pair_stages() {
-  static int cached = 0;
-  if (cached == 0) {
-    int v = kMaxStages;
-    if (const char* e = getenv("FM_GEMM_STAGES")) {
-      const int w = atoi(e);
-      if (w >= 2 && w <= kMaxStages) v = w;
-    }
-    cached = v;
-  }
-  return cached;
+  const int w = options().gemm_stages;
+  return (w >= 2 && w <= kMaxStages) ? w : kDefaultStages;
 }
 
-// Scratch of the balanced tail: per pair one partial accumulator (256 x 256 fp32: a pair leaves
-// at most one tile unfinished) and the deposit counters.  One set per device, resident while the library is loaded; it is lent to one
-// stream at a time (kernels of one stream run in order, so they can share it) and handed to
-// another stream only once the last kernel that used it has finished.  A launch that cannot have
-// it simply deals whole tiles.
-constexpr int kSkMaxPairs = 80;
-constexpr size_t kSkFloats = (size_t)kSkMaxPairs * 2 * 128 * 256;
-static __device__ __align__(256) float g_sk_ws[kSkFloats];
-static __device__ unsigned int g_sk_cnt[kSkMaxPairs * 4];
-
-struct SkScratch {
-  float* ws = nullptr;
-  unsigned int* cnt = nullptr;
-  cudaStream_t owner = nullptr;
-  bool owned = false;
-  cudaEvent_t last_use = nullptr;
-};
-
-// Returns the scratch if `stream` may use it for the launch being prepared, else nullptr.
-SkScratch* sk_acquire(cudaStream_t stream) {
-  static std::mutex mu;
-  static SkScratch per_dev[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  std::lock_guard<std::mutex> lock(mu);
-  SkScratch& s = per_dev[dev];
-  if (s.ws == nullptr) {
-    void *a = nullptr, *b = nullptr;
-    if (cudaGetSymbolAddress(&a, g_sk_ws) != cudaSuccess ||
-        cudaGetSymbolAddress(&b, g_sk_cnt) != cudaSuccess ||
-        cudaEventCreateWithFlags(&s.last_use, cudaEventDisableTiming) != cudaSuccess) {
-      cudaGetLastError();
-      return nullptr;
-    }
-    s.ws = static_cast<float*>(a);
-    s.cnt = static_cast<unsigned int*>(b);
-  }
-  if (s.owned && s.owner != stream) {
-    if (cudaEventQuery(s.last_use) != cudaSuccess) {
-      cudaGetLastError();
-      return nullptr;  // still in use by another stream
-    }
-  }
-  s.owner = stream;
-  s.owned = true;
-  return &s;
-}
-
-// Tile order of a symmetric list: FM_GEMM_STRIP=<w> selects column strips of width w
-// (tile_schedule.cuh has the reasoning: fewer distinct panels per wave, hence fewer DRAM reads,
-// once the triangle has more than ~16 tile columns).  The default stays the column order: on
-// B200 the 8192^2 and 16384 x 8192 products ran at the same speed in both orders (they are bound
-// by the tensor pipe, not by DRAM), and the DRAM traffic of the strip order has not been profiled.
+// Tile order of a symmetric list: column strips of width w (tile_schedule.cuh has the reasoning:
+// fewer distinct panels per wave, hence fewer DRAM reads, once the triangle has more than ~16
+// tile columns) or plain column order (0).
 int strip_width(const GemmParams& p) {
-  if (!p.sym) return 0;
-  const char* e = getenv("FM_GEMM_STRIP");
-  if (e == nullptr) return 0;
-  const int w = atoi(e);
-  return (w > 0 && w <= 64) ? w : 0;
-}
-
-bool sk_enabled() {
-  const char* e = getenv("FM_GEMM_BALANCE");  // read per call: lets one process compare both
-  return !(e && atoi(e) == 0);
-}
-
-// Fills the schedule fields of `p` and returns the number of CTA pairs to launch.
-int plan_schedule(GemmParams& p, int max_pairs, cudaStream_t stream, SkScratch** used) {
-  const int T = p.num_tiles;
-  int P = T < max_pairs ? T : max_pairs;
-  p.sk_dp_tiles = T;
-  p.sk_per = 0;
-  p.sk_total = 0;
-  p.sk_ws = nullptr;
-  p.sk_cnt = nullptr;
-  *used = nullptr;
-  if (!sk_enabled() || max_pairs > kSkMaxPairs) return P;
-  int dp_tiles = 0, per = 0;
-  long long total = 0;
-  if (!plan_balance(T, p.num_kb, max_pairs, &dp_tiles, &per, &total)) return P;
-  SkScratch* sc = sk_acquire(stream);
-  if (sc == nullptr) return P;
-  p.sk_dp_tiles = dp_tiles;
-  p.sk_total = total;
-  p.sk_per = per;
-  p.sk_ws = sc->ws;
-  p.sk_cnt = sc->cnt;
-  *used = sc;
-  return max_pairs;
-}
-
-template <typename T>
-int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int max_pairs,
-            cudaStream_t stream) {
-  SkScratch* used = nullptr;
-  const int pairs = plan_schedule(p, max_pairs, stream, &used);
-  p.stages = pair_stages();
-  const int kSmemBytes = smem_bytes(p.stages);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(2 * pairs));
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T>, tmA, tmB, p));
-  if (used != nullptr) FM_CUDA_CHECK(cudaEventRecord(used->last_use, stream));
-  return FM_OK;
+  if (!p.sym || p.batch > 1) return 0;
+  const int w = options().gemm_strip;
+  if (w < 0) return 0;  // by size: the column order until the strip order shows a gain
+  return w <= 64 ? w : 0;
 }
 
 // Clusters of two CTAs that can be resident at once on the current device (0 if unknown).
@@ -431,14 +347,13 @@ int max_pairs_for() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
   if (cached[dev] == 0) {
-    const int kSmemBytes = smem_bytes(pair_stages());
     if (cudaFuncSetAttribute(gemm_tc2_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smem_bytes(kMaxStages)) != cudaSuccess)
       return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2);
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.dynamicSmemBytes = smem_bytes(kDefaultStages);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
@@ -456,6 +371,61 @@ int max_pairs_for() {
   return cached[dev];
 }
 
+// Whether (and how) a list of `tiles` tiles of `num_kb` K blocks is balanced on `max_pairs` pairs.
+// Depends on the extents and the device only, never on what else is running.
+bool balance_plan(int tiles, int num_kb, int max_pairs, int batch, int* dp_tiles, int* per,
+                  long long* total) {
+  if (batch > 1 || !options().gemm_balance || max_pairs <= 0) return false;
+  if ((size_t)max_pairs * 4 * sizeof(unsigned int) > kSkCntBytes) return false;
+  return plan_balance(tiles, num_kb, max_pairs, dp_tiles, per, total);
+}
+
+template <typename T>
+int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int max_pairs,
+            void* sk_ws, size_t sk_bytes, cudaStream_t stream) {
+  const int T_all = p.num_tiles;
+  int pairs = T_all < max_pairs ? T_all : max_pairs;
+  p.sk_dp_tiles = T_all;
+  p.sk_per = 0;
+  p.sk_total = 0;
+  p.sk_ws = nullptr;
+  p.sk_cnt = nullptr;
+  int dp_tiles = 0, per = 0;
+  long long total = 0;
+  const size_t need = kSkCntBytes + (size_t)max_pairs * 2 * kSkPartBytes;
+  if (sk_ws != nullptr && sk_bytes >= need && (reinterpret_cast<uintptr_t>(sk_ws) & 255u) == 0 &&
+      balance_plan(T_all, p.num_kb, max_pairs, p.batch, &dp_tiles, &per, &total)) {
+    p.sk_dp_tiles = dp_tiles;
+    p.sk_total = total;
+    p.sk_per = per;
+    p.sk_cnt = static_cast<unsigned int*>(sk_ws);
+    p.sk_ws = reinterpret_cast<float*>(static_cast<char*>(sk_ws) + kSkCntBytes);
+    pairs = max_pairs;
+    // the deposit counters start every launch at zero, whatever an earlier launch left behind
+    FM_CUDA_CHECK(cudaMemsetAsync(p.sk_cnt, 0, kSkCntBytes, stream));
+  }
+  p.stages = pair_stages();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem_bytes(p.stages);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.numAttrs = 1;
+  if (options().pdl) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  cfg.attrs = attr;
+  FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T>, tmA, tmB, p));
+  return FM_OK;
+}
+
 }  // namespace
 
 int gemm_tc2_tiles(int64_t M, int64_t N, int sym) {
@@ -466,16 +436,27 @@ int gemm_tc2_max_pairs(int dtype) {
   return dtype == FM_BF16 ? max_pairs_for<__nv_bfloat16>() : max_pairs_for<__half>();
 }
 
+size_t gemm_tc2_sk_bytes(int dtype, int64_t M, int64_t N, int64_t K, int sym) {
+  const int max_pairs = gemm_tc2_max_pairs(dtype);
+  int dp_tiles = 0, per = 0;
+  long long total = 0;
+  if (!balance_plan(gemm_tc2_tiles(M, N, sym), (int)((K + BK - 1) / BK), max_pairs, 1, &dp_tiles,
+                    &per, &total))
+    return 0;
+  return kSkCntBytes + (size_t)max_pairs * 2 * kSkPartBytes;
+}
+
 // `p` arrives filled except for the schedule fields, which depend on the tile shape.
 int gemm_tc2_launch(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
-                    cudaStream_t stream) {
+                    void* sk_ws, size_t sk_bytes, cudaStream_t stream) {
   p.tiles_m = (p.M + 255) / 256;
-  p.num_tiles = gemm_tc2_tiles(p.M, p.N, p.sym);
+  p.tiles_per_batch = gemm_tc2_tiles(p.M, p.N, p.sym);
+  p.num_tiles = p.tiles_per_batch * p.batch;
   p.strip_w = strip_width(p);
   const int max_pairs = gemm_tc2_max_pairs(dtype);
   if (max_pairs <= 0) return fail(FM_ERR_CUDA, "no resident CTA pair possible for the GEMM kernel");
-  return dtype == FM_BF16 ? launch2<__nv_bfloat16>(tmA, tmB, p, max_pairs, stream)
-                          : launch2<__half>(tmA, tmB, p, max_pairs, stream);
+  return dtype == FM_BF16 ? launch2<__nv_bfloat16>(tmA, tmB, p, max_pairs, sk_ws, sk_bytes, stream)
+                          : launch2<__half>(tmA, tmB, p, max_pairs, sk_ws, sk_bytes, stream);
 }
 
 }  // namespace fm

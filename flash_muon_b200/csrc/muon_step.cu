@@ -12,6 +12,8 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "gemm_common.cuh"
+#include "muon_kernels.cuh"
 
 namespace fm {
 namespace {
@@ -67,18 +69,39 @@ int validate_group(const fm_muon_group& g, int gi) {
     return fail(FM_ERR_INVALID, "group %d: null array", gi);
   if (g.lanes < 1 || g.lanes > kMaxLanes)
     return fail(FM_ERR_INVALID, "group %d: lanes must be 1..%d", gi, kMaxLanes);
+  if (g.batch < 1 || g.batch > kMaxGemmBatch)
+    return fail(FM_ERR_INVALID, "group %d: batch must be 1..%d", gi, kMaxGemmBatch);
   if (g.ns_steps < 0) return fail(FM_ERR_INVALID, "group %d: negative ns_steps", gi);
   for (int i = 0; i < g.count; ++i) {
     if (!g.params[i] || !g.grads[i] || !g.momentum[i])
       return fail(FM_ERR_INVALID, "group %d: null tensor pointer at %d", gi, i);
     if (g.rows[i] < 0 || g.cols[i] < 0) return fail(FM_ERR_INVALID, "group %d: negative size at %d", gi, i);
   }
-  for (int b = 0; b < 2 * g.lanes; ++b)
+  for (int b = 0; b < 2 * g.lanes * g.batch; ++b)
     if (!g.slots[b]) return fail(FM_ERR_INVALID, "group %d: null update slot %d", gi, b);
   return FM_OK;
 }
 
+inline int64_t small_dim(const fm_muon_group& g, int i) { return g.rows[i] < g.cols[i] ? g.rows[i] : g.cols[i]; }
+inline int64_t large_dim(const fm_muon_group& g, int i) { return g.rows[i] < g.cols[i] ? g.cols[i] : g.rows[i]; }
+
+// Matrices [i, end) of the group that go through Newton-Schulz together: up to `batch`
+// consecutive non-empty matrices with the same smaller and larger dimension.
+int chunk_end(const fm_muon_group& g, int i) {
+  int e = i + 1;
+  if (g.rows[i] * g.cols[i] == 0) return e;
+  while (e < g.count && e - i < g.batch && g.rows[e] * g.cols[e] != 0 &&
+         small_dim(g, e) == small_dim(g, i) && large_dim(g, e) == large_dim(g, i))
+    ++e;
+  return e;
+}
+
 }  // namespace
+
+int newtonschulz_batched(const void* const* G, const int64_t* rows, const int64_t* cols, int count,
+                         int g_dtype, int steps, void* const* out, void* workspace,
+                         size_t workspace_bytes, int flags, cudaStream_t stream);
+
 }  // namespace fm
 
 extern "C" int fm_muon_step(const fm_muon_group* groups, int ngroups, void* const* workspaces,
@@ -90,12 +113,18 @@ extern "C" int fm_muon_step(const fm_muon_group* groups, int ngroups, void* cons
   if (!workspaces) return fail(FM_ERR_INVALID, "null workspace list");
   int max_lanes = 1;
   for (int gi = 0; gi < ngroups; ++gi) {
-    const int rc = validate_group(groups[gi], gi);
+    const fm_muon_group& g = groups[gi];
+    const int rc = validate_group(g, gi);
     if (rc != FM_OK) return rc;
-    if (groups[gi].count > 0 && groups[gi].lanes > max_lanes) max_lanes = groups[gi].lanes;
-    for (int i = 0; i < groups[gi].count; ++i)
-      if (fm_ns_workspace_bytes(groups[gi].rows[i], groups[gi].cols[i]) > workspace_bytes)
-        return fail(FM_ERR_WORKSPACE, "group %d: matrix %d needs a larger Newton-Schulz workspace", gi, i);
+    if (g.count > 0 && g.lanes > max_lanes) max_lanes = g.lanes;
+    for (int i = 0; i < g.count;) {
+      const int e = chunk_end(g, i);
+      if (g.rows[i] * g.cols[i] != 0 &&
+          fm_ns_batched_workspace_bytes(e - i, g.rows[i], g.cols[i]) > workspace_bytes)
+        return fail(FM_ERR_WORKSPACE, "group %d: matrices %d..%d need a larger Newton-Schulz workspace",
+                    gi, i, e - 1);
+      i = e;
+    }
   }
   for (int l = 0; l < max_lanes; ++l)
     if (!workspaces[l]) return fail(FM_ERR_INVALID, "null workspace for lane %d", l);
@@ -124,42 +153,66 @@ extern "C" int fm_muon_step(const fm_muon_group* groups, int ngroups, void* cons
     }
     return true;
   };
+  const size_t pfloats = fm_norm_scratch_floats();
 
   for (int gi = 0; gi < ngroups && rc == FM_OK; ++gi) {
     const fm_muon_group& g = groups[gi];
-    const int nl = g.lanes, nbuf = 2 * g.lanes;
+    const int nl = g.lanes, nset = 2 * g.lanes;
     bool have_upd[kMaxSlots] = {false};
-    // decay + update of matrix i, whose update lies in slot b, on the side stream
-    auto update = [&](int i, int b) {
-      if (!cuda_ok(cudaStreamWaitEvent(st->side, st->ns_done[b], 0), "cudaStreamWaitEvent")) return;
-      void* p = g.params[i];
-      const void* u = g.slots[b];
-      const int64_t n = g.rows[i] * g.cols[i];
-      const double alpha = g.alphas[i];
-      if (!keep(fm_update_multi(&p, &u, &n, &alpha, 1, g.p_dtype, g.decay, st->side))) return;
-      if (cuda_ok(cudaEventRecord(st->upd_done[b], st->side), "cudaEventRecord")) have_upd[b] = true;
-    };
-    int prev = -1;
-    for (int i = 0; i < g.count && rc == FM_OK; ++i) {
-      const int cur = i % nbuf;
-      cudaStream_t lane = lanes[cur % nl];
-      if (have_upd[cur]) {  // slot `cur` is free once the update that read it has run
-        if (!cuda_ok(cudaStreamWaitEvent(lane, st->upd_done[cur], 0), "cudaStreamWaitEvent")) break;
-        have_upd[cur] = false;
+    // decay + update of matrices [i0, i1), whose updates lie in slot set `set`, on the side stream
+    auto update = [&](int i0, int i1, int set) {
+      if (!cuda_ok(cudaStreamWaitEvent(st->side, st->ns_done[set], 0), "cudaStreamWaitEvent")) return;
+      void* p[kMaxGemmBatch];
+      const void* u[kMaxGemmBatch];
+      int64_t n[kMaxGemmBatch];
+      double alpha[kMaxGemmBatch];
+      for (int i = i0; i < i1; ++i) {
+        p[i - i0] = g.params[i];
+        u[i - i0] = g.slots[set * g.batch + (i - i0)];
+        n[i - i0] = g.rows[i] * g.cols[i];
+        alpha[i - i0] = g.alphas[i];
       }
-      const int64_t n = g.rows[i] * g.cols[i];
-      if (!keep(fm_momentum(g.grads[i], g.momentum[i], n, g.g_dtype, g.momentum_coef, g.nesterov, lane)))
-        break;
-      const void* src = g.nesterov ? g.grads[i] : g.momentum[i];
-      if (n > 0 && !keep(fm_newtonschulz(src, g.rows[i], g.cols[i], g.cols[i], g.g_dtype, g.ns_steps,
-                                         g.slots[cur], workspaces[cur % nl], workspace_bytes,
-                                         FM_NS_FAITHFUL, lane)))
-        break;
-      if (!cuda_ok(cudaEventRecord(st->ns_done[cur], lane), "cudaEventRecord")) break;
-      if (prev >= 0) update(i - 1, prev);
-      prev = cur;
+      if (!keep(fm_update_multi(p, u, n, alpha, i1 - i0, g.p_dtype, g.decay, st->side))) return;
+      if (cuda_ok(cudaEventRecord(st->upd_done[set], st->side), "cudaEventRecord")) have_upd[set] = true;
+    };
+    int prev_i0 = -1, prev_i1 = -1, prev_set = -1;
+    int chunk = 0;
+    for (int i0 = 0; i0 < g.count && rc == FM_OK; ++chunk) {
+      const int i1 = chunk_end(g, i0);
+      const int cnt = i1 - i0;
+      const int set = chunk % nset;
+      cudaStream_t lane = lanes[set % nl];
+      if (have_upd[set]) {  // the slots of `set` are free once the update that read them has run
+        if (!cuda_ok(cudaStreamWaitEvent(lane, st->upd_done[set], 0), "cudaStreamWaitEvent")) break;
+        have_upd[set] = false;
+      }
+      if (g.rows[i0] * g.cols[i0] != 0) {
+        char* ws = static_cast<char*>(workspaces[set % nl]);
+        float* partials = reinterpret_cast<float*>(
+            ws + fm_ns_batched_partials_offset(cnt, g.rows[i0], g.cols[i0]));
+        MomentumItem mi[kMaxGemmBatch];
+        const void* src[kMaxGemmBatch];
+        void* dst[kMaxGemmBatch];
+        for (int j = 0; j < cnt; ++j) {
+          mi[j].grad = g.grads[i0 + j];
+          mi[j].buf = g.momentum[i0 + j];
+          mi[j].n = g.rows[i0 + j] * g.cols[i0 + j];
+          mi[j].partials = partials + (size_t)j * pfloats;
+          src[j] = g.nesterov ? g.grads[i0 + j] : g.momentum[i0 + j];
+          dst[j] = g.slots[set * g.batch + j];
+        }
+        // momentum + Nesterov, leaving the partial sums of the norm behind (muon.py:99-100, :23)
+        if (!keep(momentum_batch(mi, cnt, g.g_dtype, g.momentum_coef, g.nesterov, lane))) break;
+        if (!keep(newtonschulz_batched(src, g.rows + i0, g.cols + i0, cnt, g.g_dtype, g.ns_steps, dst,
+                                       ws, workspace_bytes, FM_NS_FAITHFUL | FM_NS_SUMSQ_READY, lane)))
+          break;
+      }
+      if (!cuda_ok(cudaEventRecord(st->ns_done[set], lane), "cudaEventRecord")) break;
+      if (prev_set >= 0) update(prev_i0, prev_i1, prev_set);
+      prev_i0 = i0; prev_i1 = i1; prev_set = set;
+      i0 = i1;
     }
-    if (rc == FM_OK && prev >= 0) update(g.count - 1, prev);
+    if (rc == FM_OK && prev_set >= 0) update(prev_i0, prev_i1, prev_set);
   }
 
   // join, also after an error: the caller's stream is again the only one with work pending

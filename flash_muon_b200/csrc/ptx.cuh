@@ -61,6 +61,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while its
+// predecessor in the stream still runs; grid_dep_wait() returns once that predecessor has
+// completed and its memory operations are visible (at once if there is nothing to wait for).
+// Everything before the wait must not touch memory the predecessor writes.
+__device__ __forceinline__ void grid_dep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets the next kernel of the stream be scheduled once every CTA of this grid has issued it (or
+// exited).  Only a scheduling hint: the dependent still waits in grid_dep_wait() for completion.
+__device__ __forceinline__ void grid_dep_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

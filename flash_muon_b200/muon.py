@@ -4,10 +4,15 @@ Same parameter grouping (by ``numel``), same round-robin ownership (rank ``r`` o
 ``params[base + r]`` of every round), same order of operations and the same rounding points.
 What differs is how the device work is issued:
 
-* momentum + Nesterov is one fused kernel (``fm_momentum``) instead of two ``lerp_`` launches;
+* momentum + Nesterov is one fused kernel (``fm_momentum``) instead of two ``lerp_`` launches; it
+  also leaves the partial sums of the Frobenius norm behind, so Newton-Schulz does not read the
+  matrix once more for ``X.norm()`` (flash_muon/muon.py:23);
 * Newton-Schulz is one C-ABI call whose last GEMM epilogue writes the flat update straight into
   this rank's slot of the gather buffer (no ``.flatten()`` copy, no staging tensor);
-* rounds rotate through four gather buffers, so a round may fill its slot while older rounds
+* matrices too small to fill the GPU (a 1024-wide product is 10 tiles for 74 CTA pairs) go
+  through Newton-Schulz several at a time: every GEMM of the iteration is one launch over the
+  whole batch (``fm_newtonschulz_batched``);
+* rounds rotate through several gather buffers, so a round may fill its slot while older rounds
   are still being gathered and applied;
 * the all-gather (flash_muon/muon.py:106-108) overlaps the next round's Newton-Schulz like the
   reference's ``async_op=True`` call.  Inside one box it is done by DMA copy engines pushing
@@ -20,12 +25,16 @@ What differs is how the device work is issued:
   stream so that this HBM-bound pass runs under the tensor-core work of the following rounds;
 * with the copy-engine exchange the OWNER applies decay + update to its replica and pushes the
   updated parameter into the replicas of its peers, instead of every rank gathering and applying
-  every update: replicas are bit-identical before the step and the update is deterministic, so
-  the result is the same, but a rank streams only its share of the parameters through HBM
-  (``FM_MUON_EXCHANGE=updates`` keeps the gather of updates);
+  every update.  That equals the reference only while all replicas hold the same bits before the
+  step, which is checked once when the exchange is set up (a mismatch selects the gather of
+  updates, as does ``FM_MUON_EXCHANGE=updates``);
 * with ``world_size == 1`` and no hooks the whole step is one C call (``fm_muon_step``), which
   does the stream and event bookkeeping of the round loop inside the library
   (``FM_MUON_NATIVE=0`` keeps the loop below).
+
+Numel groups are walked from the largest to the smallest (the reference walks a Python set,
+flash_muon/muon.py:68; groups are independent): the last round of a step, whose exchange nothing
+can hide, is then a small matrix.
 """
 from __future__ import annotations
 
@@ -54,6 +63,12 @@ class Muon(torch.optim.Optimizer):
         lr, weight_decay, momentum, nesterov, ns_steps, rank, world_size.
     With ``world_size == 1`` no process group is needed (the reference still calls the
     collective); otherwise the default ``torch.distributed`` group must be initialised with NCCL.
+
+    ``param_groups`` carries exactly the reference's keys (``update_buffer``,
+    ``update_buffer_views`` and the hyper-parameters), so ``state_dict()`` has the reference's
+    layout and a checkpoint written by the reference loads (``load_state_dict`` matches numel
+    groups by the width of their ``update_buffer``).  The additional gather buffers the rotation
+    needs live outside ``param_groups`` and are never part of a checkpoint.
     """
 
     # Device of the gather buffers ("cuda" = the current CUDA device, flash_muon/muon.py:69).
@@ -61,13 +76,16 @@ class Muon(torch.optim.Optimizer):
     # Apply the decay + update of a finished round on a second stream, under the next GEMMs.
     _overlap_updates = True
     # Rounds rotate over several streams ("lanes"): the GEMM kernels are persistent and
-    # statically scheduled, so a kernel's last wave leaves SMs idle, and a matrix with
-    # min(rows, cols) <= 1024 fills at most 36 of 148 SMs; independent matrices in flight on
-    # other streams take the idle SMs.  Two lanes for large matrices, four for small ones, two
-    # gather buffers per lane.  Needs _overlap_updates (event-ordered rounds).
+    # statically scheduled, so a kernel's last wave leaves SMs idle; independent matrices in
+    # flight on other streams take the idle SMs.  Two gather buffers per lane.
     _two_lanes = True          # False: a single compute stream
-    _small_dim = 1536          # groups whose matrices are all at most this narrow get 4 lanes
+    _small_dim = 1536          # round loop: groups at most this narrow get 4 lanes
     _large_lanes = 2           # lanes of the other groups
+    _max_batch = 16            # matrices per batched Newton-Schulz pass (single-call step)
+    # Host-side deadline of the copy-engine exchange: a peer that has not taken part in a step
+    # this long after the step was enqueued is taken for gone (NCCL's watchdog default is of
+    # the same order).  FM_MUON_PEER_TIMEOUT=<seconds> overrides it, 0 switches it off.
+    _peer_timeout_s = 600.0
 
     def __init__(self, params, lr=0.02, weight_decay=0.01, momentum=0.95, nesterov=True,
                  ns_steps=5, rank=None, world_size=None):
@@ -79,90 +97,204 @@ class Muon(torch.optim.Optimizer):
                         ns_steps=ns_steps)
         params: list[Tensor] = [*params]
         param_groups = []
-        # one group per distinct numel (flash_muon/muon.py:68); sorted so that every rank walks
-        # the groups in the same order whatever its hash seed
-        for size in sorted({p.numel() for p in params}):
-            # the reference has one gather buffer per group; rounds here rotate through two per
-            # compute stream, so a round never waits for the buffer of an older one
-            members = [p for p in params if p.numel() == size]
-            narrow = max(min(p.size(0), p.numel() // max(p.size(0), 1)) for p in members)
-            lanes = 4 if narrow <= self._small_dim else self._large_lanes
-            bs = [torch.empty(world_size, size, dtype=torch.bfloat16, device=self._buffer_device)
-                  for _ in range(2 * lanes)]
-            vs = [[b[i] for i in range(world_size)] for b in bs]
-            group = dict(params=members, lanes=lanes,
-                         update_buffer=bs[0], update_buffer_views=vs[0],
-                         update_buffer_alt=bs[1], update_buffer_alt_views=vs[1],
-                         update_buffer_more=bs[2:], update_buffer_more_views=vs[2:])
+        # one group per distinct numel (flash_muon/muon.py:68), largest first, the same order on
+        # every rank whatever its hash seed
+        for size in sorted({p.numel() for p in params}, reverse=True):
+            b = torch.empty(world_size, size, dtype=torch.bfloat16, device=self._buffer_device)
+            group = dict(params=[p for p in params if p.numel() == size],
+                         update_buffer=b, update_buffer_views=[b[i] for i in range(world_size)])
             param_groups.append(group)
         super().__init__(param_groups, defaults)
+        self._pool: dict = {}         # group index -> gather buffers beyond group["update_buffer"]
         self._workspaces: dict = {}   # lane -> Newton-Schulz scratch
         self._lane = 0
-        self._peer = None          # PeerGather once set up; False if NCCL is to be used
+        self._peer = None             # PeerGather once set up; False if NCCL is to be used
+        self._peer_recheck = False    # every rank went through load_state_dict: re-validate together
+        self._push_params = True      # replicas were bit-identical when the exchange was set up
+        self._watchdog = None
 
     # ------------------------------------------------------------------ helpers
+    @staticmethod
+    def _narrow(group) -> int:
+        """Largest smaller-dimension among the matrices of a group (conv filters as size(0) x rest)."""
+        return max(min(p.size(0), p.numel() // max(p.size(0), 1)) for p in group["params"])
+
+    def _pairs(self) -> int:
+        """CTA pairs of the device (one 256 x 256 tile in flight each)."""
+        n = getattr(self, "_pairs_cached", None)
+        if n is None:
+            buf = self.param_groups[0]["update_buffer"]
+            n = torch.cuda.get_device_properties(buf.device).multi_processor_count // 2 if buf.is_cuda else 74
+            self._pairs_cached = n
+        return n
+
+    def _plan(self, group, native: bool) -> tuple[int, int]:
+        """(lanes, batch) of a group: the single-call step batches narrow matrices (as many as
+        fill one wave of CTA pairs with the tiles of ``X @ X.T``) over two lanes; the round loop
+        runs one matrix per round, narrow ones over four lanes."""
+        narrow = self._narrow(group)
+        if native:
+            t = -(-narrow // 256)
+            batch = max(1, min(self._max_batch, self._pairs() // (t * (t + 1) // 2)))
+            forced = os.environ.get("FM_MUON_BATCH")
+            if forced:
+                batch = max(1, min(16, int(forced)))
+            return 2, batch
+        return (4 if narrow <= self._small_dim else self._large_lanes), 1
+
+    def _group_buffers(self, gi: int, count: int):
+        """``count`` gather buffers of group ``gi`` in rotation order and their per-rank views: the
+        group's own ``update_buffer`` first, the rest from a pool outside ``param_groups``."""
+        group = self.param_groups[gi]
+        first = group["update_buffer"]
+        pool = self._pool.get(gi)
+        if pool is None or any(b.shape != first.shape or b.device != first.device for b in pool):
+            pool = self._pool[gi] = []
+        while len(pool) < count - 1:
+            pool.append(torch.empty_like(first))
+        bufs = [first, *pool[:count - 1]]
+        views = [group["update_buffer_views"]] + [[b[i] for i in range(self.world_size)]
+                                                  for b in pool[:count - 1]]
+        return bufs, views
+
     def _ns_workspace(self, rows: int, cols: int, device) -> Tensor:
         """Newton-Schulz scratch of the lane (stream) the current round runs on; grows to the
-        largest matrix that lane has seen (groups are visited in order of size)."""
+        largest matrix that lane has seen."""
         need = newtonschulz_workspace_bytes(rows, cols)
         ws = self._workspaces.get(self._lane)
         if ws is None or ws.numel() < need or ws.device != device:
             self._workspaces[self._lane] = ws = torch.empty(need, dtype=torch.uint8, device=device)
         return ws
 
-    def _momentum(self, g: Tensor, buf: Tensor, momentum: float, nesterov: bool) -> Tensor:
+    def _momentum(self, g: Tensor, buf: Tensor, momentum: float, nesterov: bool,
+                  partials: int = 0) -> Tensor:
         # buf.lerp_(g, 1 - momentum); g.lerp_(buf, momentum)           (flash_muon/muon.py:99-100)
+        # `partials`: device address that receives the partial sums of squares of the result
         assert g.is_contiguous(), "Muon gradients must be contiguous"
         check(lib.fm_momentum(g.data_ptr(), buf.data_ptr(), g.numel(), dtype_code(g.dtype),
-                              float(momentum), 1 if nesterov else 0, current_stream_ptr(g.device)))
+                              float(momentum), 1 if nesterov else 0, partials or None,
+                              current_stream_ptr(g.device)))
         return g if nesterov else buf
 
-    def _orthogonalize(self, g: Tensor, out: Tensor, steps: int) -> None:
+    def _orthogonalize(self, g: Tensor, out: Tensor, steps: int, sumsq_ready: bool = False) -> None:
         # fast_newtonschulz(g, steps).flatten() written into `out`     (flash_muon/muon.py:103)
         rows, cols = g.shape
         fast_newtonschulz(g, steps=steps, out=out.view(rows, cols),
-                          workspace=self._ns_workspace(rows, cols, g.device))
+                          workspace=self._ns_workspace(rows, cols, g.device), sumsq_ready=sumsq_ready)
 
     def _all_gather(self, buffer: Tensor, slot: Tensor):
         # in place: `slot` is row `rank` of `buffer`                    (flash_muon/muon.py:108)
         return dist.all_gather_into_tensor(buffer, slot, async_op=True)
 
-    @staticmethod
-    def _group_buffers(group):
-        """(buffers, views) of a group in rotation order."""
-        bufs = [group["update_buffer"], group["update_buffer_alt"], *group["update_buffer_more"]]
-        views = [group["update_buffer_views"], group["update_buffer_alt_views"],
-                 *group["update_buffer_more_views"]]
-        return bufs, views
+    # ------------------------------------------------------------------ checkpoints
+    def load_state_dict(self, state_dict) -> None:
+        """Loads a checkpoint of this class or of the reference (flash_muon/muon.py:68-73 writes
+        one ``param_groups`` entry per numel with ``update_buffer`` of shape
+        ``[world_size, numel]``, in the iteration order of a Python set).  Saved groups are matched
+        to this optimizer's groups by that width, and gather buffers that come back on another
+        device or for another world size are replaced."""
+        saved = list(state_dict["param_groups"])
+        ours = [g["params"][0].numel() for g in self.param_groups]
+        if len(saved) == len(ours) and all(torch.is_tensor(g.get("update_buffer")) for g in saved):
+            widths = [g["update_buffer"].size(-1) for g in saved]
+            if widths != ours and sorted(widths) == sorted(ours):
+                saved = [saved[widths.index(n)] for n in ours]
+                state_dict = dict(state_dict, param_groups=saved)
+        super().load_state_dict(state_dict)
+        for gi, group in enumerate(self.param_groups):
+            p0 = group["params"][0]
+            want_dev = p0.device if p0.is_cuda else torch.device(self._buffer_device)
+            b = group.get("update_buffer")
+            ok = (torch.is_tensor(b) and b.dtype == torch.bfloat16 and b.is_contiguous()
+                  and tuple(b.shape) == (self.world_size, p0.numel())
+                  and b.device.type == want_dev.type
+                  and (want_dev.index is None or b.device == want_dev))
+            if not ok:
+                group["update_buffer"] = b = torch.empty(self.world_size, p0.numel(),
+                                                         dtype=torch.bfloat16, device=want_dev)
+            group["update_buffer_views"] = [b[i] for i in range(self.world_size)]
+        self._pool = {}
+        self._peer_recheck = True
+
+    def close(self) -> None:
+        """Releases what the copy-engine exchange mapped from the peers (collective in spirit:
+        call it on every rank, with no step in flight)."""
+        if self._watchdog is not None:
+            self._watchdog.stop()
+            self._watchdog = None
+        if self._peer:
+            self._peer.close()
+        self._peer = None
+
+    # ------------------------------------------------------------------ exchange set-up
+    def _replicas_identical(self, device) -> bool:
+        """One all-reduce over a checksum of the raw bits of every parameter: the owner-pushes-
+        the-parameter exchange equals the reference only if all replicas agree beforehand."""
+        sums = []
+        for group in self.param_groups:
+            for p in group["params"]:
+                bits = p.detach().reshape(-1).view(
+                    {1: torch.int8, 2: torch.int16, 4: torch.int32, 8: torch.int64}[p.element_size()])
+                sums.append(bits.sum(dtype=torch.int64))
+        h = torch.stack(sums).to(device)
+        lo, hi = h.clone(), h.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        return bool(torch.equal(lo, hi))
+
+    def _peer_pointers(self):
+        bufs = [[b.data_ptr() for b in self._group_buffers(gi, 2 * self._plan(g, False)[0])[0]]
+                for gi, g in enumerate(self.param_groups)]
+        pars = [[p.data_ptr() for p in g["params"]] for g in self.param_groups]
+        return bufs, pars
 
     def _peer_gather(self):
         """The copy-engine all-gather, set up collectively on first use (None: use NCCL)."""
         if self._peer:
-            # load_state_dict() replaces the gather buffers: the exported addresses are stale then
-            now = [[b.data_ptr() for b in self._group_buffers(g)[0]] for g in self.param_groups]
-            nowp = [[p.data_ptr() for p in g["params"]] for g in self.param_groups]
-            if now != self._peer.buffer_ptrs or nowp != self._peer.param_ptrs:
-                self._peer = None
+            # Addresses exported to the peers must still be the live ones.  Setting the exchange
+            # up again is collective, so it may only be decided together: after load_state_dict
+            # (which every rank calls) the ranks agree by all-reduce; a rank whose tensors moved
+            # on its own cannot drag the others in and has to fail instead.
+            bufs, pars = self._peer_pointers()
+            stale = bufs != self._peer.buffer_ptrs or pars != self._peer.param_ptrs
+            if self._peer_recheck:
+                self._peer_recheck = False
+                flag = torch.tensor([int(stale)], device=self.param_groups[0]["update_buffer"].device)
+                dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+                if int(flag.item()):
+                    self.close()
+            elif stale:
+                raise RuntimeError(
+                    "parameter or gather-buffer storage moved since the peer exchange was set up; "
+                    "call load_state_dict (or close()) on every rank so that all ranks set it up again")
         if self._peer is None:
             self._peer = False
+            self._peer_recheck = False
             want = os.environ.get("FM_MUON_GATHER", "peer") != "nccl"
             if want and self.world_size > 1 and self.param_groups[0]["update_buffer"].is_cuda:
-                from .peer_gather import CudaOps, PeerGather
+                from .peer_gather import CudaOps, PeerGather, Watchdog
                 ok, peer = 1, None
+                device = self.param_groups[0]["update_buffer"].device
+                timeout = float(os.environ.get("FM_MUON_PEER_TIMEOUT", self._peer_timeout_s or 0)) or None
                 try:
-                    device = self.param_groups[0]["update_buffer"].device
-                    peer = PeerGather(self.rank, self.world_size,
-                                      [[b.data_ptr() for b in self._group_buffers(g)[0]]
-                                       for g in self.param_groups], CudaOps(device),
-                                      param_addrs=[[p.data_ptr() for p in g["params"]]
-                                                   for g in self.param_groups])
+                    bufs, pars = self._peer_pointers()
+                    peer = PeerGather(self.rank, self.world_size, bufs, CudaOps(device),
+                                      param_addrs=pars, timeout_s=timeout)
                 except Exception as exc:  # same decision on every rank, taken below
                     ok = 0
                     warnings.warn(f"peer all-gather unavailable ({exc}); using NCCL")
-                flag = torch.tensor([ok], device=self.param_groups[0]["update_buffer"].device)
+                flag = torch.tensor([ok], device=device)
                 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
                 if int(flag.item()) == 1:
                     self._peer = peer
+                    self._push_params = self._replicas_identical(device)
+                    if not self._push_params:
+                        warnings.warn("parameter replicas differ between ranks: every rank applies "
+                                      "every update (as the reference does) instead of receiving "
+                                      "the owner's updated parameter")
+                    if timeout is not None:
+                        self._watchdog = Watchdog(peer, device)
+                        self._watchdog.start()
         return self._peer or None
 
     def _apply_updates(self, params_world, views, lr, weight_decay):
@@ -210,28 +342,27 @@ class Muon(torch.optim.Optimizer):
                 return self._step(grad_ready, on_applied)
         return self._step(grad_ready, on_applied)
 
+    def _stock_device_ops(self) -> bool:
+        cls = type(self)
+        return (cls._momentum is Muon._momentum and cls._orthogonalize is Muon._orthogonalize
+                and cls._apply_updates is Muon._apply_updates)
+
     def _native_step(self) -> bool:
         """The whole step as one C call (``fm_muon_step``) when there is nothing for Python to do
         between rounds: one rank, no hooks, the stock device operations.  Returns False (having
-        done nothing) when the round loop below has to run instead.  Same kernels in the same
-        order per matrix as the loop, so the parameters come out bit-identical; what goes away
-        is the per-round stream and event bookkeeping on the host."""
-        cls = type(self)
-        if not (self._overlap_updates and self._two_lanes
-                and cls._momentum is Muon._momentum and cls._orthogonalize is Muon._orthogonalize
-                and cls._apply_updates is Muon._apply_updates
+        done nothing) when the round loop below has to run instead.  Same arithmetic per matrix
+        as the loop, so the parameters come out bit-identical; what goes away is the per-round
+        stream and event bookkeeping on the host, and narrow matrices share their launches."""
+        if not (self._overlap_updates and self._two_lanes and self._stock_device_ops()
                 and os.environ.get("FM_MUON_NATIVE", "1") != "0"):
             return False
         device = self.param_groups[0]["update_buffer"].device
         plan = []
-        need = 0
-        for group in self.param_groups:
+        for gi, group in enumerate(self.param_groups):
             params = group["params"]
             if not params:
                 continue
             p0 = params[0]
-            if len(self._group_buffers(group)[0]) < 2 * group.get("lanes", 2):
-                return False
             for p in params:
                 g = p.grad
                 assert g is not None
@@ -239,10 +370,12 @@ class Muon(torch.optim.Optimizer):
                         or not g.is_contiguous() or not p.is_contiguous() or g.device != device
                         or p.dtype not in _NATIVE_DTYPES or g.dtype not in _NATIVE_DTYPES):
                     return False
-            plan.append(group)
+            plan.append((gi, group))
         groups = (MuonGroup * max(len(plan), 1))()
         keep = []  # ctypes arrays must outlive the call
-        for gs, group in zip(groups, plan):
+        need = 0
+        nlanes = 1
+        for gs, (gi, group) in zip(groups, plan):
             params = group["params"]
             n = len(params)
             lr, nes = group["lr"], group["nesterov"]
@@ -254,9 +387,12 @@ class Muon(torch.optim.Optimizer):
                 bufs.append(state["momentum_buffer"].data_ptr())
             rows = [p.grad.size(0) for p in params]
             cols = [p.grad.numel() // max(r, 1) for p, r in zip(params, rows)]
-            need = max([need] + [newtonschulz_workspace_bytes(r, c) for r, c in set(zip(rows, cols))])
-            lanes = group.get("lanes", 2)
-            slots, _ = self._group_buffers(group)
+            lanes, batch = self._plan(group, True)
+            batch = min(batch, n)
+            nlanes = max(nlanes, lanes)
+            need = max([need] + [int(lib.fm_ns_batched_workspace_bytes(batch, r, c))
+                                 for r, c in set(zip(rows, cols))])
+            slots, _ = self._group_buffers(gi, 2 * lanes * batch)
             arrays = (
                 (ctypes.c_void_p * n)(*[p.data_ptr() for p in params]),
                 (ctypes.c_void_p * n)(*[p.grad.data_ptr() for p in params]),
@@ -264,16 +400,15 @@ class Muon(torch.optim.Optimizer):
                 (ctypes.c_int64 * n)(*rows),
                 (ctypes.c_int64 * n)(*cols),
                 (ctypes.c_double * n)(*[-lr * max(1, p.size(-2) / p.size(-1)) ** 0.5 for p in params]),
-                (ctypes.c_void_p * (2 * lanes))(*[b.data_ptr() for b in slots[:2 * lanes]]),
+                (ctypes.c_void_p * len(slots))(*[b.data_ptr() for b in slots]),
             )
             keep.append(arrays)
             (gs.params, gs.grads, gs.momentum, gs.rows, gs.cols, gs.alphas, gs.slots) = arrays
-            gs.count, gs.lanes = n, lanes
+            gs.count, gs.lanes, gs.batch = n, lanes, batch
             gs.p_dtype, gs.g_dtype = dtype_code(params[0].dtype), dtype_code(params[0].grad.dtype)
             gs.nesterov, gs.ns_steps = (1 if nes else 0), int(group["ns_steps"])
             gs.momentum_coef = float(group["momentum"])
             gs.decay = 1 - lr * group["weight_decay"]
-        nlanes = max([g.get("lanes", 2) for g in plan], default=1)
         for lane in range(nlanes):
             ws = self._workspaces.get(lane)
             if ws is None or ws.numel() < need or ws.device != device:
@@ -304,14 +439,18 @@ class Muon(torch.optim.Optimizer):
                     st.wait_stream(main)        # gradients produced on the caller's stream
         peer = self._peer_gather() if (ws > 1 and type(self)._all_gather is Muon._all_gather) else None
         # Owner-applies-and-pushes-the-parameter exchange (see peer_gather.py): needs the peer
-        # set-up and the event-ordered update stream; FM_MUON_EXCHANGE=updates keeps the
-        # reference's "gather the updates, every rank applies all of them".
-        push_params_ok = peer is not None and overlap and \
+        # set-up, the event-ordered update stream and replicas that agreed at set-up;
+        # FM_MUON_EXCHANGE=updates keeps the reference's "gather the updates, every rank applies
+        # all of them".
+        push_params_ok = peer is not None and overlap and self._push_params and \
             os.environ.get("FM_MUON_EXCHANGE", "params") != "updates"
+        # the fused momentum kernel can leave the partial sums of the norm for Newton-Schulz
+        fused = self._stock_device_ops() and overlap
         if peer is not None:
             peer.begin_step(torch.cuda.current_stream(self.param_groups[0]["update_buffer"].device))
         for gi, group in enumerate(self.param_groups):
-            buffers, views = self._group_buffers(group)
+            nlanes = self._plan(group, False)[0]
+            buffers, views = self._group_buffers(gi, 2 * nlanes)
             nbuf = len(buffers)
             params: list[Tensor] = group["params"]
             handle = None
@@ -369,7 +508,6 @@ class Muon(torch.optim.Optimizer):
                 cur = round_idx % nbuf
                 slot = views[cur][self.rank]
                 # buffer `cur` always travels on lane `cur % nlanes`
-                nlanes = group.get("lanes", 2)
                 lane = lanes[cur % nlanes] if lanes is not None else (main if overlap else None)
                 self._lane = (cur % nlanes) if lanes is not None else 0
                 with (torch.cuda.stream(lane) if lanes is not None else contextlib.nullcontext()):
@@ -388,10 +526,20 @@ class Muon(torch.optim.Optimizer):
                         if "momentum_buffer" not in state:
                             state["momentum_buffer"] = torch.zeros_like(g)
                         buf: Tensor = state["momentum_buffer"]
-                        g = self._momentum(g, buf, group["momentum"], group["nesterov"])
-                        if g.ndim == 4:  # for the case of conv filters
-                            g = g.view(len(g), -1)
-                        self._orthogonalize(g, slot, group["ns_steps"])
+                        rows = g.size(0)
+                        cols = g.numel() // max(rows, 1)
+                        if fused and g.ndim in (2, 4) and g.numel() > 0 and g.dtype in _NATIVE_DTYPES:
+                            wsp = self._ns_workspace(rows, cols, g.device)
+                            part = wsp.data_ptr() + int(lib.fm_ns_partials_offset(rows, cols))
+                            g = self._momentum(g, buf, group["momentum"], group["nesterov"], part)
+                            if g.ndim == 4:  # for the case of conv filters
+                                g = g.view(len(g), -1)
+                            self._orthogonalize(g, slot, group["ns_steps"], True)
+                        else:
+                            g = self._momentum(g, buf, group["momentum"], group["nesterov"])
+                            if g.ndim == 4:  # for the case of conv filters
+                                g = g.view(len(g), -1)
+                            self._orthogonalize(g, slot, group["ns_steps"])
                         if overlap:
                             ns_done[cur] = torch.cuda.Event()
                             ns_done[cur].record(lane)

@@ -32,10 +32,22 @@ Process-to-process addresses come from CUDA IPC handles exchanged once through t
 All device-facing operations go through a small ``ops`` object (``CudaOps`` here); the protocol
 itself is plain bookkeeping, which lets a test drive it against simulated streams under
 arbitrary interleavings.
+
+A stream that waits on a flag waits for ever if the peer that should write it has left (an
+exception between steps, a crashed process): unlike an NCCL collective, a stream memory operation
+has no timeout.  The deadline is therefore kept on the host.  Every step leaves a record of the
+flag values its streams wait for and an event behind its last operation; ``poll()`` -- called by a
+small watchdog thread once a second and by every ``begin_step`` -- looks at the oldest unfinished
+step, and if it is older than ``timeout_s`` it writes the awaited values into this rank's own flag
+words from a separate stream, so that every parked stream drains, marks the exchange ``failed``
+and makes the next ``begin_step`` raise.  All awaited flags live in this rank's own memory, so the
+release needs nothing from the peer that is gone.
 """
 from __future__ import annotations
 
 import ctypes
+import threading
+import time
 
 import torch
 import torch.distributed as dist
@@ -43,6 +55,11 @@ import torch.distributed as dist
 from ._lib import check, lib
 
 READY, ACK = 0, 1
+
+
+class PeerExchangeError(RuntimeError):
+    """A peer did not take part in a step within the deadline; the parameters of that step are
+    not to be trusted (the parked streams were released without their data)."""
 
 
 class CudaOps:
@@ -91,6 +108,12 @@ class CudaOps:
     def wait_event(self, stream, event) -> None:
         stream.wait_event(event)
 
+    def query(self, event) -> bool:
+        return event.query()
+
+    def now(self) -> float:
+        return time.monotonic()
+
     # -- stream-ordered memory operations
     def wait32_geq(self, stream, addr: int, value: int) -> None:
         check(lib.fm_stream_wait32_geq(addr, value, stream.cuda_stream))
@@ -114,7 +137,7 @@ class PeerRound:
         st = o.ops.current_stream()
         for r, s in zip(self.producers, self.seqs):
             if r != o.rank:
-                o.ops.wait32_geq(st, o.flag_addr(o.rank, self.gi, self.b, READY, r), s)
+                o._wait(st, o.flag_addr(o.rank, self.gi, self.b, READY, r), s)
 
     def done(self) -> None:
         o = self.owner
@@ -131,8 +154,14 @@ class PeerGather:
     ``[world_size, numel]``, rows contiguous) on this rank."""
 
     def __init__(self, rank: int, world_size: int, buffer_addrs: list[list[int]], ops,
-                 param_addrs: list[list[int]] | None = None):
+                 param_addrs: list[list[int]] | None = None, timeout_s: float | None = None):
         self.rank, self.ws, self.ops = rank, world_size, ops
+        self.timeout_s = timeout_s          # None: no deadline
+        self.failed: str | None = None      # set by the watchdog; begin_step raises once it is
+        self._inflight: list = []           # per unfinished step: [event, enqueue time, waits]
+        self._waits: dict = {}              # flag address -> largest value this step waits for
+        self._lock = threading.Lock()
+        self._release_stream = None
         self.ngroups = len(buffer_addrs)
         self.nbuf = max(len(bl) for bl in buffer_addrs)
         self.buffer_ptrs = [list(bl) for bl in buffer_addrs]
@@ -160,7 +189,10 @@ class PeerGather:
         self._step_waited: set = set()
         self._step_events: list = []
         ops.barrier()  # nobody writes a flag before everybody has zeroed and mapped them
-        self.streams = {q: ops.new_stream() for q in range(world_size) if q != rank}
+        # peers in rotated order, so that the ranks of a box do not all push to rank 0 first
+        self.streams = {q: ops.new_stream()
+                        for q in ((rank + i) % world_size for i in range(1, world_size))}
+        self._release_stream = ops.new_stream()
         # host-side mirror of the use counters: seq[group][buffer][producer]
         self.seq = [[[0] * world_size for _ in range(self.nbuf)] for _ in range(self.ngroups)]
         # events of this rank's copies out of its slot, per (group, buffer)
@@ -172,9 +204,50 @@ class PeerGather:
     def step_flag_addr(self, holder: int, idx: int) -> int:
         return self._flag_base[holder] + 4 * (self._step_flags + idx)
 
+    def _wait(self, stream, addr: int, value: int) -> None:
+        """A flag wait of the current step, remembered so that the watchdog can release it."""
+        with self._lock:
+            if value > self._waits.get(addr, 0):
+                self._waits[addr] = value
+        self.ops.wait32_geq(stream, addr, value)
+
+    def poll(self, now: float | None = None) -> bool:
+        """Host-side deadline: True if the exchange is healthy.  Looks at the oldest step whose
+        streams have not drained; past the deadline it writes every flag value that step (and any
+        later one) waits for, so that the streams drain, and marks the exchange failed."""
+        with self._lock:
+            if self.failed:
+                return False
+            while self._inflight and self.ops.query(self._inflight[0][0]):
+                self._inflight.pop(0)
+            if not self._inflight or self.timeout_s is None:
+                return True
+            now = self.ops.now() if now is None else now
+            if now - self._inflight[0][1] <= self.timeout_s:
+                return True
+            release: dict = {}
+            for _, _, waits in self._inflight:
+                for addr, value in waits.items():
+                    release[addr] = max(value, release.get(addr, 0))
+            for addr, value in self._waits.items():   # a step still being enqueued
+                release[addr] = max(value, release.get(addr, 0))
+            for addr, value in release.items():
+                self.ops.write32(self._release_stream, addr, value)
+            self.failed = (f"rank {self.rank}: a peer did not take part in the parameter exchange "
+                           f"within {self.timeout_s} s; the waiting streams were released")
+            self._inflight = []
+            return False
+
+    def check(self) -> None:
+        if not self.poll():
+            raise PeerExchangeError(self.failed)
+
     def begin_step(self, stream) -> None:
         """``stream`` carries whatever this rank did with its parameters before the step: once it
         gets here, peers may write updated parameters into this rank's replicas."""
+        self.check()
+        with self._lock:
+            self._waits = {}
         self.step_no += 1
         self._step_waited = set()
         self._step_events = []
@@ -187,6 +260,9 @@ class PeerGather:
         for ev in self._step_events:
             self.ops.wait_event(stream, ev)
         self._step_events = []
+        with self._lock:
+            self._inflight.append([self.ops.record(stream), self.ops.now(), self._waits])
+            self._waits = {}
 
     def param_addr(self, holder: int, gi: int, index: int) -> int:
         return self._param_base[holder][gi][index]
@@ -214,12 +290,12 @@ class PeerGather:
             for q, st in self.streams.items():
                 self.ops.wait_event(st, ready)
                 # q has consumed what I sent it in the previous use of buffer / flag row b
-                self.ops.wait32_geq(st, self.flag_addr(self.rank, gi, b, ACK, q), s - 1)
+                self._wait(st, self.flag_addr(self.rank, gi, b, ACK, q), s - 1)
                 if param_index is None:
                     dst = self._buf_base[q][gi][b] + self.rank * nbytes
                 else:
                     if q not in self._step_waited:  # q has entered this step
-                        self.ops.wait32_geq(st, self.step_flag_addr(self.rank, q), self.step_no)
+                        self._wait(st, self.step_flag_addr(self.rank, q), self.step_no)
                         self._step_waited.add(q)
                     dst = self.param_addr(q, gi, param_index)
                 self.ops.copy(st, dst, slot_addr, nbytes)
@@ -231,3 +307,26 @@ class PeerGather:
 
     def close(self) -> None:
         lib.fm_ipc_close_all()
+
+
+class Watchdog(threading.Thread):
+    """Calls ``PeerGather.poll`` once a second from a daemon thread, so that the deadline also
+    fires while the main thread is blocked in a synchronisation on the parked streams."""
+
+    def __init__(self, gather: PeerGather, device, period_s: float = 1.0):
+        super().__init__(daemon=True, name="flash-muon-peer-watchdog")
+        self.gather, self.device, self.period_s = gather, device, period_s
+        self._halt = threading.Event()
+
+    def run(self) -> None:
+        if self.device is not None:
+            torch.cuda.set_device(self.device)
+        while not self._halt.wait(self.period_s):
+            try:
+                if not self.gather.poll():
+                    return
+            except Exception:  # noqa: BLE001 -- a dying context must not take the process along
+                return
+
+    def stop(self) -> None:
+        self._halt.set()

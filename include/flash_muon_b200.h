@@ -8,9 +8,12 @@
  * Conventions
  *  - Every function returns an fm_status (0 = ok, negative = error).  Nothing throws.
  *  - All data pointers are DEVICE pointers owned by the caller; no entry point allocates or frees
- *    memory and nothing synchronises unless stated.  The library's device image carries two
- *    fixed scratch arrays that exist on every GPU that loads it: ~21 MB for the partial sums of
- *    the balanced GEMM tail and ~38 MB for fm_newtonschulz_static.
+ *    memory and nothing synchronises unless stated.  Scratch memory is passed in by the caller
+ *    (the *_workspace_bytes functions give its size); calls that may overlap on the GPU need
+ *    distinct scratch.  The one exception is fm_newtonschulz_static, whose ~38 MB scratch array
+ *    is part of the library's device image and exists on every GPU that loads it.
+ *  - What a call launches depends on its arguments and the process-wide options only, never on
+ *    what else is running: the same call gives the same bits every time.
  *  - `stream` is a cudaStream_t passed as void* (0 = the legacy default stream).  All work of a
  *    call is enqueued on that stream of the CURRENT device.
  *  - Leading dimensions and strides are in ELEMENTS.
@@ -38,14 +41,29 @@ typedef enum {
 
 typedef enum { FM_BF16 = 0, FM_F16 = 1, FM_F32 = 2 } fm_dtype;
 
-/* flags of fm_newtonschulz */
+/* flags of fm_newtonschulz (bit mask) */
 enum {
-  FM_NS_FAITHFUL = 0, /* reproduce every intermediate rounding of the reference formulation */
-  FM_NS_PRECISE = 1   /* one rounding per fused epilogue (closer to exact, further from reference) */
+  FM_NS_FAITHFUL = 0,   /* reproduce every intermediate rounding of the reference formulation */
+  FM_NS_PRECISE = 1,    /* one rounding per fused epilogue (closer to exact, further from reference) */
+  FM_NS_SUMSQ_READY = 2 /* fm_momentum already left the partial sums of squares in the workspace */
 };
 
 /* Library version: major * 10000 + minor * 100 + patch. */
 int fm_version(void);
+
+/*
+ * Process-wide tuning switches, for experiments and A/B comparisons (the defaults are the
+ * product).  Names: "gemm_impl" (0 by size, 1 single-CTA kernel, 2 CTA-pair kernel), "gemm_bn"
+ * (tile width of the single-CTA kernel: 0 by size, 128, 256), "gemm_stages" (ring depth of the
+ * pair kernel, 0 = default), "gemm_balance" (0: never cut the tail of a tile list by K blocks),
+ * "gemm_strip" (tile order of symmetric lists: -1 by size, 0 column order, w = strips of w tile
+ * columns), "pdl" (0: no programmatic dependent launch).  Initial values come from the
+ * environment variables FM_GEMM_IMPL, FM_GEMM_BN, FM_GEMM_STAGES, FM_GEMM_BALANCE, FM_GEMM_STRIP
+ * and FM_PDL, read once.  Stands in for the autotune table of the reference
+ * (flash_muon/matmul_transpose_triton.py:6-18); not thread-safe against concurrent launches.
+ */
+int fm_set_option(const char* name, int value);
+int fm_get_option(const char* name, int* value);
 
 /* Message of the last error raised on the calling thread ("" if none). */
 const char* fm_last_error(void);
@@ -66,9 +84,14 @@ int fm_device_status(unsigned int* code);
  * Replaces: mmt_kernel + matmul_transpose_assign, flash_muon/matmul_transpose_triton.py:19-101.
  * bf16/f16 with ldx % 8 == 0 and a 16-byte aligned x run on tcgen05 tensor cores; f32 and other
  * layouts run on an exact-fp32 FFMA kernel.
+ * workspace (may be null): fm_syrk_workspace_bytes(M, K, dtype) bytes of 256-byte aligned device
+ * scratch.  Long tile lists (e.g. 8192 x 8192) use it to split the last tiles by K so that no SM
+ * idles through a partial last wave; without it every tile is computed whole.  Both schedules
+ * are deterministic; they differ in the order of the fp32 sums of the split tiles.
  */
+size_t fm_syrk_workspace_bytes(int64_t M, int64_t K, int dtype);
 int fm_syrk(const void* x, void* y, int64_t M, int64_t K, int64_t ldx, int64_t ldy_row,
-            int64_t ldy_col, int dtype, void* stream);
+            int64_t ldy_col, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * General C[M,N] = A[M,K] * B[N,K]^T (+ fused epilogue), bf16/f16, both operands row-major with
@@ -92,8 +115,11 @@ int fm_syrk_poly(const void* x, int64_t ldx, int64_t M, int64_t K, const void* D
                  float alpha, float beta, void* out, int64_t ldo, int dtype, int precise,
                  void* stream);
 
-/* Bytes of device workspace fm_newtonschulz needs for a rows x cols input (0 on bad sizes). */
+/* Bytes of device workspace fm_newtonschulz needs for a rows x cols input (0 on bad sizes), and
+ * the byte offset inside it of the fm_norm_scratch_floats() partial sums that fm_momentum may
+ * fill ahead of the call (FM_NS_SUMSQ_READY). */
 size_t fm_ns_workspace_bytes(int64_t rows, int64_t cols);
+size_t fm_ns_partials_offset(int64_t rows, int64_t cols);
 
 /*
  * out = Newton-Schulz orthogonalisation of G (rows x cols, row pitch ldg, dtype g_dtype), `steps`
@@ -105,6 +131,26 @@ size_t fm_ns_workspace_bytes(int64_t rows, int64_t cols);
  */
 int fm_newtonschulz(const void* G, int64_t rows, int64_t cols, int64_t ldg, int g_dtype, int steps,
                     void* out, void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/*
+ * Newton-Schulz of `count` (1..16) matrices in one pass: G[i] is rows[i] x cols[i] (contiguous,
+ * dtype g_dtype), out[i] the bf16 result of the same shape.  All matrices must have the same
+ * smaller and the same larger dimension (a 4096 x 1024 and a 1024 x 4096 matrix may share a
+ * batch, as they share a numel group in flash_muon/muon.py:68).  Every GEMM of the iteration is
+ * ONE launch whose tile list covers all matrices, so matrices that are too small to fill the GPU
+ * on their own (a 1024 x 1024 product is 10 tiles for 74 CTA pairs) share it, and the number of
+ * launches per matrix drops by `count`.  The arithmetic per matrix is that of fm_newtonschulz:
+ * results are bit-identical.  Replaces: `count` calls of fast_newtonschulz,
+ * flash_muon/muon.py:6-33, for the matrices a rank owns in consecutive rounds (muon.py:90-103).
+ * Workspace: fm_ns_batched_workspace_bytes(count, rows[0], cols[0]); with FM_NS_SUMSQ_READY the
+ * partial sums of matrix i are expected at fm_ns_batched_partials_offset(...) +
+ * i * fm_norm_scratch_floats() * sizeof(float).
+ */
+size_t fm_ns_batched_workspace_bytes(int count, int64_t rows, int64_t cols);
+size_t fm_ns_batched_partials_offset(int count, int64_t rows, int64_t cols);
+int fm_newtonschulz_batched(const void* const* G, const int64_t* rows, const int64_t* cols,
+                            int count, int g_dtype, int steps, void* const* out, void* workspace,
+                            size_t workspace_bytes, int flags, void* stream);
 
 /*
  * fm_newtonschulz for callers that cannot allocate device memory -- a plugin running inside a
@@ -143,9 +189,13 @@ size_t fm_norm_scratch_floats(void);
  *   buf <- lerp(buf, grad, 1 - momentum);  grad <- nesterov ? lerp(grad, buf, momentum) : grad
  * each lerp rounded to `dtype` like torch's lerp_.  With nesterov == 0 grad is left untouched and
  * the caller uses buf.  Replaces: flash_muon/muon.py:99-100.
+ * sumsq_partials (may be null): fm_norm_scratch_floats() floats that receive the partial sums of
+ * squares of the tensor Newton-Schulz reads next (grad if nesterov, else buf) -- bit for bit the
+ * partial sums fm_normalize would compute itself, so that fm_newtonschulz with FM_NS_SUMSQ_READY
+ * can skip its own pass over the matrix (flash_muon/muon.py:23 reads it once more for the norm).
  */
 int fm_momentum(void* grad, void* buf, int64_t n, int dtype, double momentum, int nesterov,
-                void* stream);
+                float* sumsq_partials, void* stream);
 
 /*
  * Fused decoupled weight decay + scaled update over `count` tensors in one launch:
@@ -160,9 +210,12 @@ int fm_update_multi(void* const* params, const void* const* updates, const int64
  * Matrix i is params[i] (dtype p_dtype) with gradient grads[i] and momentum buffer momentum[i]
  * (both g_dtype), all contiguous, seen as rows[i] x cols[i] (conv filters: size(0) x the rest,
  * flash_muon/muon.py:101-102).  alphas[i] = -lr * sqrt(max(1, size(-2) / size(-1))) of the
- * ORIGINAL shape (muon.py:89), decay = 1 - lr * weight_decay (muon.py:87).  slots holds
- * 2 * lanes device buffers of rows*cols bf16 each: the update of round i is written to slot
- * i mod (2 * lanes), the role the reference's update_buffer plays (muon.py:69, :103).
+ * ORIGINAL shape (muon.py:89), decay = 1 - lr * weight_decay (muon.py:87).  Consecutive matrices
+ * with the same smaller and larger dimension go through Newton-Schulz `batch` at a time
+ * (fm_newtonschulz_batched: one launch per GEMM for all of them; batch = 1 for matrices that fill
+ * the GPU on their own).  slots holds 2 * lanes * batch device buffers of rows*cols bf16 each: the
+ * update of matrix j of pass c is written to slot (c mod (2 * lanes)) * batch + j, the role the
+ * reference's update_buffer plays (muon.py:69, :103).
  */
 typedef struct {
   void* const* params;
@@ -177,6 +230,8 @@ typedef struct {
   int32_t nesterov;
   int32_t ns_steps;
   int32_t lanes;        /* 1..4 streams the rounds of this group rotate over */
+  int32_t batch;        /* 1..16 consecutive same-shape matrices per Newton-Schulz pass */
+  int32_t reserved;     /* 0 */
   double momentum_coef; /* mu of muon.py:99-100 */
   double decay;
   void* const* slots;
@@ -193,7 +248,8 @@ typedef struct {
  * order them); all of them wait for `stream` at entry and `stream` waits for all of them before
  * the call returns, so to the caller the step is ordinary work on `stream`.
  * workspaces: HOST array of one device buffer of workspace_bytes per lane (as many as the
- * largest `lanes` of the groups), each at least fm_ns_workspace_bytes of the largest matrix.
+ * largest `lanes` of the groups), each at least fm_ns_batched_workspace_bytes(batch, rows, cols)
+ * of the most demanding group.
  * One step at a time per device.  gradients are overwritten when nesterov != 0, as by the
  * reference (muon.py:100).
  */

@@ -29,6 +29,22 @@ def golden():
     return torch.load(ROOT / "tests" / "golden" / "reference_outputs.pt")
 
 
+@pytest.fixture
+def options():
+    """Sets tuning switches of the library (``fm_set_option``) for one test and restores them."""
+    from flash_muon_b200 import _lib
+    saved = {}
+
+    def set_option(name: str, value: int) -> None:
+        if name not in saved:
+            saved[name] = _lib.get_option(name)
+        _lib.set_option(name, value)
+
+    yield set_option
+    for name, value in saved.items():
+        _lib.set_option(name, value)
+
+
 def rel_fro(a: torch.Tensor, b: torch.Tensor) -> float:
     """||a - b||_F / ||b||_F in float64."""
     a = a.detach().double().cpu()

@@ -17,8 +17,9 @@ def declared_symbols():
 
 def test_header_declares_the_hot_path_entry_points():
     syms = declared_symbols()
-    for name in ("fm_syrk", "fm_newtonschulz", "fm_momentum", "fm_update_multi", "fm_gemm_nt",
-                 "fm_syrk_poly", "fm_normalize", "fm_ns_workspace_bytes", "fm_device_status"):
+    for name in ("fm_syrk", "fm_newtonschulz", "fm_newtonschulz_batched", "fm_momentum",
+                 "fm_update_multi", "fm_gemm_nt", "fm_syrk_poly", "fm_normalize",
+                 "fm_ns_workspace_bytes", "fm_device_status", "fm_muon_step"):
         assert name in syms
 
 
@@ -47,7 +48,7 @@ def test_host_only_calls():
     """Entry points that touch no device."""
     from flash_muon_b200 import _lib
     lib = _lib.lib
-    assert lib.fm_version() >= 100
+    assert lib.fm_version() >= 200
     assert lib.fm_norm_scratch_floats() >= 1
     assert lib.fm_ns_workspace_bytes(0, 4) == 0
     m, k = 1024, 4096
@@ -55,11 +56,24 @@ def test_host_only_calls():
     assert need == lib.fm_ns_workspace_bytes(k, m)          # tall = wide transposed
     assert need >= (4 * m * k + 2 * m * m) * 2              # X, XT double-buffered + A + B
     # argument validation happens before any CUDA call
-    assert lib.fm_syrk(None, None, 4, 4, 4, 4, 1, 0, None) == -1
+    assert lib.fm_syrk(None, None, 4, 4, 4, 4, 1, 0, None, 0, None) == -1
     assert b"null" in lib.fm_last_error()
     assert lib.fm_newtonschulz(None, 4, 4, 4, 0, 5, None, None, 0, 0, None) == -1
-    assert lib.fm_momentum(None, None, 4, 0, 0.95, 1, None) == -1
+    assert lib.fm_momentum(None, None, 4, 0, 0.95, 1, None, None) == -1
     assert lib.fm_update_multi(None, None, None, None, -1, 0, 1.0, None) == -1
+    assert lib.fm_newtonschulz_batched(None, None, None, 2, 0, 5, None, None, 0, 0, None) == -1
+    assert lib.fm_ns_batched_workspace_bytes(0, 8, 8) == 0 == lib.fm_ns_batched_workspace_bytes(17, 8, 8)
+    assert lib.fm_ns_batched_workspace_bytes(1, m, k) == need
+    assert lib.fm_ns_batched_workspace_bytes(4, m, k) >= 4 * (4 * m * k + 2 * m * m) * 2
+    assert lib.fm_ns_partials_offset(m, k) + 4 * lib.fm_norm_scratch_floats() <= need
+    # tuning switches: unknown names are refused, known ones round-trip
+    assert lib.fm_set_option(b"no_such_switch", 1) == -1
+    v = ctypes.c_int(-5)
+    assert lib.fm_get_option(b"gemm_balance", ctypes.byref(v)) == 0 and v.value in (0, 1)
+    old = v.value
+    assert lib.fm_set_option(b"gemm_balance", 0) == 0
+    assert lib.fm_get_option(b"gemm_balance", ctypes.byref(v)) == 0 and v.value == 0
+    assert lib.fm_set_option(b"gemm_balance", old) == 0
     assert lib.fm_newtonschulz_static(None, 0, 4, 4, 0, 5, None, 0, None) == -1
     assert lib.fm_newtonschulz_static(None, 2048, 2048, 2048, 0, 5, None, 0, None) == -5
     assert b"1024 x 4096" in lib.fm_last_error()
@@ -75,9 +89,9 @@ def test_whole_step_call_validates_before_any_cuda_call():
     """fm_muon_step rejects malformed groups on the host; the struct layout is the header's."""
     import ctypes
     from flash_muon_b200 import _lib
-    assert ctypes.sizeof(_lib.MuonGroup) == 6 * 8 + 6 * 4 + 2 * 8 + 8
+    assert ctypes.sizeof(_lib.MuonGroup) == 6 * 8 + 8 * 4 + 2 * 8 + 8
     g = _lib.MuonGroup()
-    g.count, g.lanes = 1, 2
+    g.count, g.lanes, g.batch = 1, 2, 1
     assert _lib.lib.fm_muon_step(g, 1, None, 0, None) == -1          # null workspace list
     w = (ctypes.c_void_p * 1)(0)
     assert _lib.lib.fm_muon_step(g, 1, w, 0, None) == -1             # null arrays in the group

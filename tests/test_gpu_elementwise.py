@@ -27,7 +27,7 @@ def test_momentum_bit_exact(dt, nesterov, n, offset):
     b = _rand(n + offset, dt, 1e-3, 2)[offset:]
     g_ref, b_ref = g.clone(), b.clone()
     used = O.momentum_update(g_ref, b_ref, 0.95, nesterov)   # torch CUDA lerp_
-    check(lib.fm_momentum(g.data_ptr(), b.data_ptr(), n, dtype_code(dt), 0.95, int(nesterov), 0))
+    check(lib.fm_momentum(g.data_ptr(), b.data_ptr(), n, dtype_code(dt), 0.95, int(nesterov), None, 0))
     assert torch.equal(b, b_ref)
     assert torch.equal(g, g_ref)
     assert used.data_ptr() == (g_ref if nesterov else b_ref).data_ptr()
@@ -36,6 +36,42 @@ def test_momentum_bit_exact(dt, nesterov, n, offset):
     O.momentum_update(gc, bc, 0.95, nesterov)
     assert torch.allclose(b.cpu().float(), bc.float(), rtol=2 ** -7, atol=1e-9)
     assert torch.allclose(g.cpu().float(), gc.float(), rtol=2 ** -7, atol=1e-9)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("nesterov", [True, False])
+@pytest.mark.parametrize("rows,cols,offset", [(1024, 1024, 0), (256, 384, 0), (100, 72, 0),
+                                              (65, 63, 0), (33, 7, 1), (4096, 1024, 0)])
+def test_momentum_leaves_the_partial_sums_of_the_norm(dt, nesterov, rows, cols, offset):
+    """With a partials pointer fm_momentum also produces the partial sums of squares that
+    fm_normalize computes in its first pass -- the same floats, whether the fused kernel ran
+    (aligned tensors of a vector multiple) or the separate pass (anything else): Newton-Schulz
+    with FM_NS_SUMSQ_READY then equals the plain call bit for bit."""
+    n = rows * cols
+    g = _rand(n + offset, dt, 1e-3, 3)[offset:]
+    b = _rand(n + offset, dt, 1e-3, 4)[offset:]
+    g2, b2 = g.clone(), b.clone()
+    need = lib.fm_ns_workspace_bytes(rows, cols)
+    off = lib.fm_ns_partials_offset(rows, cols)
+    ws = torch.zeros(need, device=DEV, dtype=torch.uint8)
+    ws2 = torch.zeros(need, device=DEV, dtype=torch.uint8)
+    check(lib.fm_momentum(g.data_ptr(), b.data_ptr(), n, dtype_code(dt), 0.95, int(nesterov),
+                          ws.data_ptr() + off, 0))
+    check(lib.fm_momentum(g2.data_ptr(), b2.data_ptr(), n, dtype_code(dt), 0.95, int(nesterov), None, 0))
+    assert torch.equal(g, g2) and torch.equal(b, b2)
+    src, src2 = (g, g2) if nesterov else (b, b2)
+    out = torch.empty(rows, cols, device=DEV, dtype=torch.bfloat16)
+    out2 = torch.empty(rows, cols, device=DEV, dtype=torch.bfloat16)
+    check(lib.fm_newtonschulz(src.data_ptr(), rows, cols, cols, dtype_code(dt), 2, out.data_ptr(),
+                              ws.data_ptr(), need, _lib.FM_NS_SUMSQ_READY, 0))
+    check(lib.fm_newtonschulz(src2.data_ptr(), rows, cols, cols, dtype_code(dt), 2, out2.data_ptr(),
+                              ws2.data_ptr(), need, 0, 0))
+    nparts = max(1, min(1024, (n + 8191) // 8192))
+    p1 = ws[off:off + 4 * nparts].view(torch.float32)
+    p2 = ws2[off:off + 4 * nparts].view(torch.float32)
+    assert torch.equal(p1, p2)
+    assert torch.equal(out, out2)
+    _lib.device_status()
 
 
 @pytest.mark.parametrize("dt", DTYPES)

@@ -129,8 +129,9 @@ def test_state_dict_layout_and_side_effects():
     for g in opt.param_groups:
         assert g["update_buffer"].shape == (1, g["params"][0].numel())
         assert g["update_buffer"].dtype == torch.bfloat16 and len(g["update_buffer_views"]) == 1
-        for k in ("lr", "weight_decay", "momentum", "nesterov", "ns_steps"):
-            assert k in g
+        # exactly what the reference keeps in a group (flash_muon/muon.py:63-73)
+        assert set(g) == {"params", "lr", "weight_decay", "momentum", "nesterov", "ns_steps",
+                          "update_buffer", "update_buffer_views"}
     # p.grad was overwritten by the Nesterov lerp (flash_muon/muon.py:100)
     assert not torch.equal(ps[0].grad.cpu(), grads[0][0])
     # a learning-rate schedule is honoured: lr = 0 and no decay leaves parameters untouched
@@ -235,6 +236,53 @@ def test_state_dict_round_trip():
     torch.cuda.synchronize()
     for p, r in zip(ps, ref):
         assert torch.equal(p, r)
+
+
+def test_reference_format_checkpoint_loads_and_steps():
+    """A checkpoint laid out as the reference writes it (groups in another order, parameter ids
+    numbered along that order, gather buffers on the CPU after ``map_location="cpu"``) loads and
+    the next step equals an uninterrupted run."""
+    from test_host_logic import reference_format
+    params, grads = muon_case(2, seed=13)
+    ref, _ = run_product(params, grads, 2, **MUON_HP)
+    ps = [torch.nn.Parameter(p.to(DEV)) for p in params]
+    opt = fm.Muon(ps, rank=0, world_size=1, **MUON_HP)
+    for p, g in zip(ps, grads[0]):
+        p.grad = g.to(DEV).clone()
+    opt.step()
+    sd = reference_format(opt.state_dict())
+    opt2 = fm.Muon(ps, rank=0, world_size=1, **MUON_HP)
+    opt2.load_state_dict(sd)
+    assert all(g["update_buffer"].is_cuda for g in opt2.param_groups)
+    for p, g in zip(ps, grads[1]):
+        p.grad = g.to(DEV).clone()
+    opt2.step()
+    torch.cuda.synchronize()
+    for p, r in zip(ps, ref):
+        assert torch.equal(p, r)
+
+
+def test_large_matrices_on_two_lanes_are_run_to_run_deterministic():
+    """8192-wide matrices take the balanced GEMM tail (tiles cut by K blocks, partial sums through
+    per-lane scratch) while two of them are in flight on two streams: the schedule depends on the
+    shape only, so two runs from the same state give the same bits."""
+    shapes = [(8192, 8192)] * 3
+    g = torch.Generator(device=DEV).manual_seed(21)
+    base = [(torch.randn(*s, device=DEV, generator=g) * 0.02).bfloat16() for s in shapes]
+    grads = [(torch.randn(*s, device=DEV, generator=g) * 1e-3).bfloat16() for s in shapes]
+    assert _lib.lib.fm_syrk_workspace_bytes(8192, 8192, 0) > 0      # the balanced tail is in play
+    runs = []
+    for _ in range(2):
+        ps = [torch.nn.Parameter(p.clone()) for p in base]
+        for p, gr in zip(ps, grads):
+            p.grad = gr.clone()
+        fm.Muon(ps, rank=0, world_size=1, **MUON_HP).step()
+        torch.cuda.synchronize()
+        runs.append([p.detach().clone() for p in ps])
+        del ps
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)
+    _lib.device_status()
 
 
 def test_missing_grad_asserts():

@@ -1,8 +1,6 @@
 """Parity of the CUDA symmetric product (through the C ABI) with the oracle, the reference's golden
 outputs and a plain torch product, on BASELINE's configs and on the edge cases the reference's
 kernel handles (sizes off the tile grid, strided outputs, other dtypes)."""
-import os
-
 import pytest
 import torch
 
@@ -14,7 +12,7 @@ from oracle import muon_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-TOL = {torch.float32: 1e-5, torch.bfloat16: 1e-2, torch.float16: 1e-2}  # north-star tolerances
+TOL = {torch.float32: 1e-5, torch.bfloat16: 1e-2, torch.float16: 1e-2}  # tolerances BASELINE.json states for fp32 / 16-bit products
 
 
 def check_syrk(x, y):
@@ -75,14 +73,14 @@ ODD = [(1, 8), (7, 8), (8, 1), (100, 72), (129, 64), (257, 136), (130, 1000), (3
 @pytest.mark.parametrize("bn", ["128", "256", "pair"])
 @pytest.mark.parametrize("m,k", ODD)
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
-def test_sizes_off_the_tile_grid(m, k, dt, bn, monkeypatch):
+def test_sizes_off_the_tile_grid(m, k, dt, bn, options):
     """Every tile shape of the tensor-core family (single CTA 128x128 / 128x256, CTA pair
     256x256) on sizes that are not multiples of any of them."""
     if bn == "pair":
-        monkeypatch.setenv("FM_GEMM_IMPL", "2")
+        options("gemm_impl", 2)
     else:
-        monkeypatch.setenv("FM_GEMM_IMPL", "1")
-        monkeypatch.setenv("FM_GEMM_BN", bn)
+        options("gemm_impl", 1)
+        options("gemm_bn", int(bn))
     x = torch.randn(m, k, device=DEV, generator=torch.Generator(device=DEV).manual_seed(m * k)).to(dt)
     y = torch.full((m, m), float("nan"), device=DEV, dtype=dt)  # canary: every element written
     fm.matmul_transpose_assign(x, y)
@@ -117,38 +115,97 @@ def test_run_to_run_determinism():
     assert torch.equal(fm.matmul_transpose(x), fm.matmul_transpose(x))
 
 
-def test_balanced_tail_schedule(monkeypatch):
+def test_balanced_tail_schedule(options):
     """A tile list of several waves with a short last wave and a long K is finished by cutting
     the last tiles by K blocks (partial accumulators through fp32 scratch): same tolerance, exact
     symmetry, run-to-run determinism, and within rounding of the whole-tile schedule."""
     m, k = 3328, 5120   # 91 tiles of 256 x 256 on 74 CTA pairs, 80 K blocks
     x = (torch.randn(m, k, device=DEV, generator=torch.Generator(device=DEV).manual_seed(5)) / k ** 0.5).bfloat16()
-    monkeypatch.setenv("FM_GEMM_BALANCE", "1")
+    options("gemm_balance", 1)
+    assert _lib.lib.fm_syrk_workspace_bytes(m, k, 0) > 0      # this shape takes the balanced tail
     y = torch.full((m, m), float("nan"), device=DEV, dtype=torch.bfloat16)
     fm.matmul_transpose_assign(x, y)
     check_syrk(x, y)
     assert torch.equal(y, fm.matmul_transpose(x))
     assert torch.equal(y, fm.matmul_transpose(x))
-    monkeypatch.setenv("FM_GEMM_BALANCE", "0")
+    options("gemm_balance", 0)
+    assert _lib.lib.fm_syrk_workspace_bytes(m, k, 0) == 0
     whole = fm.matmul_transpose(x)
+    # the C entry point without scratch deals whole tiles whatever the switch says
+    options("gemm_balance", 1)
+    bare = torch.empty_like(whole)
+    _lib.check(_lib.lib.fm_syrk(x.data_ptr(), bare.data_ptr(), m, k, k, m, 1, 0, None, 0, 0))
+    assert torch.equal(bare, whole)
     assert rel_fro(y, whole) <= 2e-3
     assert rel_fro(whole, torch.matmul(x, x.T)) <= 2e-3
     _lib.device_status()
 
 
 @pytest.mark.parametrize("w", [3, 8])
-def test_strip_tile_order_gives_the_same_product(w, monkeypatch):
-    """FM_GEMM_STRIP walks the same tiles in column strips: with whole tiles (short K, no balanced
+def test_strip_tile_order_gives_the_same_product(w, options):
+    """The strip order walks the same tiles in column strips: with whole tiles (short K, no balanced
     tail) every tile is computed by the same instructions, so the product is bit-identical."""
     torch.manual_seed(4)
     x = (torch.randn(4700, 320, device=DEV) / 18).bfloat16()     # 19 tile columns, ragged edge
-    monkeypatch.setenv("FM_GEMM_IMPL", "2")
-    monkeypatch.setenv("FM_GEMM_STRIP", "0")
+    options("gemm_impl", 2)
+    options("gemm_strip", 0)
     y0 = fm.matmul_transpose(x)
-    monkeypatch.setenv("FM_GEMM_STRIP", str(w))
+    options("gemm_strip", w)
     y1 = fm.matmul_transpose(x)
     assert torch.equal(y0, y1) and torch.equal(y1, y1.T)
     assert rel_fro(y1, x.float() @ x.float().T) <= 1e-2
+    _lib.device_status()
+
+
+def test_concurrent_streams_keep_their_own_scratch():
+    """Two streams running the balanced schedule at the same time each use the scratch of their
+    own stream: both results equal the single-stream result bit for bit."""
+    m, k = 3328, 5120
+    x = (torch.randn(m, k, device=DEV, generator=torch.Generator(device=DEV).manual_seed(6)) / k ** 0.5).bfloat16()
+    ref = fm.matmul_transpose(x)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    torch.cuda.synchronize()
+    for _ in range(3):
+        for st in (s1, s2):
+            with torch.cuda.stream(st):
+                outs.append(fm.matmul_transpose(x))
+    torch.cuda.synchronize()
+    assert all(torch.equal(o, ref) for o in outs)
+    _lib.device_status()
+
+
+@pytest.mark.parametrize("pdl", [0, 1])
+def test_dependent_launches_see_their_predecessor(pdl, options):
+    """A chain of products, each reading the previous one's output, with and without programmatic
+    dependent launch: the early-started kernel must not read before its predecessor is done."""
+    options("pdl", pdl)
+    x = (torch.randn(768, 768, device=DEV, generator=torch.Generator(device=DEV).manual_seed(8)) / 28).bfloat16()
+    ref = x
+    for _ in range(6):
+        ref = (ref.float() @ ref.float().T).bfloat16()
+        ref = ref / ref.abs().max().clamp_min(1e-30).bfloat16()
+    cur = x
+    bufs = [torch.empty(768, 768, device=DEV, dtype=torch.bfloat16) for _ in range(2)]
+    # no host synchronisation inside the chain; the scaling is a torch kernel between two of ours
+    for i in range(6):
+        fm.matmul_transpose_assign(cur, bufs[i % 2])
+        cur = bufs[i % 2]
+        cur.div_(cur.abs().max().clamp_min(1e-30))
+    torch.cuda.synchronize()
+    assert rel_fro(cur, ref) <= 2e-2
+    chain = []
+    for _ in range(2):      # back-to-back products without anything in between
+        a = fm.matmul_transpose(x)
+        b = fm.matmul_transpose(a)
+        chain.append(fm.matmul_transpose(b))
+    torch.cuda.synchronize()
+    assert torch.equal(chain[0], chain[1])
+    a = fm.matmul_transpose(x)
+    torch.cuda.synchronize()
+    b = fm.matmul_transpose(a)
+    torch.cuda.synchronize()
+    assert torch.equal(chain[0], fm.matmul_transpose(b))
     _lib.device_status()
 
 

@@ -116,7 +116,8 @@ def test_whole_step_call_receives_the_reference_step_arguments(monkeypatch):
                 params=[g.params[j] for j in range(n)], grads=[g.grads[j] for j in range(n)],
                 momentum=[g.momentum[j] for j in range(n)], rows=[g.rows[j] for j in range(n)],
                 cols=[g.cols[j] for j in range(n)], alphas=[g.alphas[j] for j in range(n)],
-                slots=[g.slots[j] for j in range(2 * g.lanes)], lanes=g.lanes, p_dtype=g.p_dtype,
+                slots=[g.slots[j] for j in range(2 * g.lanes * g.batch)], lanes=g.lanes,
+                batch=g.batch, p_dtype=g.p_dtype,
                 g_dtype=g.g_dtype, nesterov=g.nesterov, ns_steps=g.ns_steps, mu=g.momentum_coef,
                 decay=g.decay))
         seen["wbytes"] = wbytes
@@ -128,7 +129,9 @@ def test_whole_step_call_receives_the_reference_step_arguments(monkeypatch):
     assert opt._native_step() is True
     assert seen["ngroups"] == len(opt.param_groups) == 3
     flat = []
-    for got, group in zip(seen["groups"], opt.param_groups):
+    # groups are walked from the largest numel down
+    assert [g["params"][0].numel() for g in opt.param_groups] == [48 * 48, 64 * 32, 16 * 72]
+    for gi, (got, group) in enumerate(zip(seen["groups"], opt.param_groups)):
         ps = group["params"]
         flat += ps
         assert got["params"] == [p.data_ptr() for p in ps]
@@ -138,15 +141,19 @@ def test_whole_step_call_receives_the_reference_step_arguments(monkeypatch):
         assert got["rows"] == [p.shape[0] for p in ps]
         assert got["cols"] == [p.numel() // p.shape[0] for p in ps]
         assert got["alphas"] == [-0.05 * max(1, p.size(-2) / p.size(-1)) ** 0.5 for p in ps]
-        bufs, _ = opt._group_buffers(group)
-        assert got["slots"] == [b.data_ptr() for b in bufs[:2 * got["lanes"]]]
+        # narrow matrices share a Newton-Schulz pass: as many as the group holds, 16 at most
+        assert got["lanes"] == 2 and got["batch"] == min(len(ps), 16)
+        bufs, _ = opt._group_buffers(gi, 2 * got["lanes"] * got["batch"])
+        assert got["slots"] == [b.data_ptr() for b in bufs]
+        assert len(set(got["slots"])) == len(got["slots"]) and bufs[0] is group["update_buffer"]
         assert (got["p_dtype"], got["g_dtype"], got["nesterov"], got["ns_steps"]) == (0, 0, 0, 3)
         assert got["mu"] == 0.9 and got["decay"] == 1 - 0.05 * 0.1
     assert sorted(id(p) for p in flat) == sorted(id(p) for p in params)
     # conv filter: 16 x 72 view, scale of the kernel dims (3 / 3 -> 1)
     conv = [g for g in seen["groups"] if g["rows"] == [16]][0]
     assert conv["cols"] == [72] and conv["alphas"] == [-0.05]
-    need = max(M.newtonschulz_workspace_bytes(r, c) for g in seen["groups"] for r, c in zip(g["rows"], g["cols"]))
+    need = max(M.lib.fm_ns_batched_workspace_bytes(g["batch"], r, c)
+               for g in seen["groups"] for r, c in zip(g["rows"], g["cols"]))
     assert seen["wbytes"] >= need and all(seen["lanes_with_workspace"])
 
     # anything the C call cannot express goes back to the round loop: strided gradients,
@@ -166,3 +173,90 @@ def test_whole_step_call_receives_the_reference_step_arguments(monkeypatch):
     params[1].grad = None
     with pytest.raises(AssertionError):
         opt._native_step()
+
+
+REFERENCE_GROUP_KEYS = {"params", "lr", "weight_decay", "momentum", "nesterov", "ns_steps",
+                        "update_buffer", "update_buffer_views"}
+
+
+def reference_format(sd):
+    """The layout flash_muon/muon.py:68-73 gives a checkpoint: one group per numel in another
+    order than this optimizer's (a Python set there, ascending here), parameter ids numbered along
+    that order, the gather buffer as a CPU tensor (as ``torch.load(map_location="cpu")`` leaves it)."""
+    groups = sorted((dict(g) for g in sd["param_groups"]), key=lambda g: g["update_buffer"].size(-1))
+    renumber, nxt = {}, 0
+    for g in groups:
+        ids = []
+        for pid in g["params"]:
+            renumber[pid] = nxt
+            ids.append(nxt)
+            nxt += 1
+        g["params"] = ids
+        b = g["update_buffer"].cpu().clone()
+        g["update_buffer"], g["update_buffer_views"] = b, [b[i] for i in range(b.size(0))]
+    # state_dict() hands out the live tensors; a checkpoint read from disk would not alias them
+    state = {renumber[k]: {n: (t.clone() if torch.is_tensor(t) else t) for n, t in v.items()}
+             for k, v in sd["state"].items()}
+    return {"state": state, "param_groups": groups}
+
+
+def test_state_dict_has_the_reference_layout_and_reference_checkpoints_load():
+    from oracle import muon_oracle as O
+
+    class CpuMuon(fm.Muon):
+        _buffer_device = "cpu"
+
+        def _momentum(self, g, buf, momentum, nesterov):
+            return O.momentum_update(g, buf, momentum, nesterov)
+
+        def _orthogonalize(self, g, out, steps):
+            out.copy_(O.newtonschulz(g, steps=steps).flatten())
+
+        def _apply_updates(self, params_world, views, lr, weight_decay):
+            for p, g in zip(params_world, views):
+                O.apply_update(p, g, lr, weight_decay)
+
+    torch.manual_seed(1)
+    shapes = [(64, 32), (32, 64), (16, 8, 3, 3), (48, 48), (64, 32), (24, 48)]
+
+    def make():
+        g = torch.Generator().manual_seed(5)
+        ps = [torch.nn.Parameter((torch.randn(*s, generator=g) * 0.02).bfloat16()) for s in shapes]
+        for p in ps:
+            p.grad = (torch.randn(*p.shape, generator=g) * 1e-3).bfloat16()
+        return ps
+
+    a = make()
+    opt = CpuMuon(a, rank=0, world_size=1)
+    opt.step()
+    sd = opt.state_dict()
+    for g in sd["param_groups"]:
+        assert set(g) == REFERENCE_GROUP_KEYS            # nothing beyond what the reference saves
+    ref_sd = reference_format(sd)
+    assert [g["update_buffer"].size(-1) for g in ref_sd["param_groups"]] != \
+        [g["update_buffer"].size(-1) for g in sd["param_groups"]]
+
+    b = make()
+    opt2 = CpuMuon(b, rank=0, world_size=1)
+    opt2.load_state_dict(ref_sd)
+    for pa, pb in zip(a, b):                             # every momentum buffer on its own parameter
+        assert torch.equal(opt.state[pa]["momentum_buffer"], opt2.state[pb]["momentum_buffer"])
+    for g in opt2.param_groups:
+        n = g["params"][0].numel()
+        assert tuple(g["update_buffer"].shape) == (1, n) and all(p.numel() == n for p in g["params"])
+    # and the next step continues as if nothing had happened
+    for pa, pb in zip(a, b):
+        pb.data.copy_(pa.data)
+        pa.grad = pb.grad.clone()
+    opt.step()
+    opt2.step()
+    for pa, pb in zip(a, b):
+        assert torch.equal(pa, pb)
+    # a checkpoint taken at another world size brings a gather buffer of the wrong height
+    wide = reference_format(opt.state_dict())
+    for g in wide["param_groups"]:
+        t = g["update_buffer"].repeat(4, 1)
+        g["update_buffer"], g["update_buffer_views"] = t, [t[i] for i in range(4)]
+    opt2.load_state_dict(wide)
+    assert all(tuple(g["update_buffer"].shape) == (1, g["params"][0].numel()) for g in opt2.param_groups)
+    opt2.step()

@@ -8,7 +8,7 @@ import random
 
 import pytest
 
-from flash_muon_b200.peer_gather import PeerGather
+from flash_muon_b200.peer_gather import PeerExchangeError, PeerGather
 
 
 class Sim:
@@ -21,6 +21,8 @@ class Sim:
         self.board = {}
         self.rng = random.Random(seed)
         self.next_addr = 1 << 20
+        self.clock = 0.0         # host time the deadline of the exchange is measured against
+        self.relaxed = False     # after a forced release the data invariants no longer hold
         self.replica_of = {}     # address of a parameter replica -> rank that holds it
         self.used = {}           # rank -> last step whose pre-step use of the replicas is over
 
@@ -29,7 +31,7 @@ class Sim:
         self.next_addr += (nbytes + 255) // 256 * 256 + 256
         return a
 
-    def run(self):
+    def run(self, allow_stuck=False):
         while True:
             ready = [s for s in self.streams if s.queue and s.queue[0].ready()]
             if not ready:
@@ -37,7 +39,8 @@ class Sim:
             s = self.rng.choice(ready)
             s.queue.pop(0).run()
         stuck = [s.name for s in self.streams if s.queue]
-        assert not stuck, f"deadlock: streams with pending work {stuck}"
+        assert allow_stuck or not stuck, f"deadlock: streams with pending work {stuck}"
+        return stuck
 
 
 class Op:
@@ -99,6 +102,12 @@ class SimOps:
     def wait_event(self, stream, event):
         stream.push(lambda: event.done, lambda: None)
 
+    def query(self, event):
+        return event.done
+
+    def now(self):
+        return self.sim.clock
+
     def wait32_geq(self, stream, addr, value):
         stream.push(lambda: self.sim.mem[addr] >= value, lambda: None)
 
@@ -109,6 +118,9 @@ class SimOps:
         def run():
             payload = self.sim.mem[src]
             old = self.sim.mem.get(dst)
+            if self.sim.relaxed:
+                self.sim.mem[dst] = payload
+                return
             if dst in self.sim.replica_of:
                 # live model state: its holder must have entered the step the value belongs to
                 q = self.sim.replica_of[dst]
@@ -122,7 +134,7 @@ class SimOps:
         stream.push(lambda: True, run)
 
 
-def build_world(ws, nbuf, numel_bytes, seed, nparams=0):
+def build_world(ws, nbuf, numel_bytes, seed, nparams=0, timeout_s=None):
     sim = Sim(ws, seed)
     opses = [SimOps(sim, r) for r in range(ws)]
     bufs = [[sim.alloc(ws * numel_bytes) for _ in range(nbuf)] for _ in range(ws)]
@@ -139,7 +151,7 @@ def build_world(ws, nbuf, numel_bytes, seed, nparams=0):
     for r, ops in enumerate(opses):
         ops.alloc_flags = lambda n, o=ops: o._prealloc
         ops.exchange = lambda obj, w, p=posted: [p[i] for i in range(w)]
-        gathers.append(PeerGather(r, ws, [bufs[r]], ops, param_addrs=[pars[r]]))
+        gathers.append(PeerGather(r, ws, [bufs[r]], ops, param_addrs=[pars[r]], timeout_s=timeout_s))
     if nparams:
         return sim, opses, bufs, gathers, pars
     return sim, opses, bufs, gathers
@@ -259,7 +271,7 @@ def test_simulation_catches_pushes_that_do_not_wait_for_the_step_flag():
     assert caught > 0
 
 
-def drive_params(ws, nbuf, lanes, seed, drop_step_wait=False):
+def drive_params(ws, nbuf, lanes, seed, drop_step_wait=False, absent=(), timeout_s=None, steps=2):
     """The owner applies the update and pushes the parameter into its peers' replicas.  Between
     two steps every rank 'uses' its replicas (as a forward/backward pass would): no replica may
     change before its rank has entered the next step, every replica must carry the owner's value
@@ -267,7 +279,8 @@ def drive_params(ws, nbuf, lanes, seed, drop_step_wait=False):
     nbytes = 64
     rounds = 5
     nparams = rounds * ws - 1                      # last round: one rank idle
-    sim, opses, bufs, gathers, pars = build_world(ws, nbuf, nbytes, seed, nparams=nparams)
+    sim, opses, bufs, gathers, pars = build_world(ws, nbuf, nbytes, seed, nparams=nparams,
+                                                  timeout_s=timeout_s)
     for r in range(ws):
         for i in range(nparams):
             sim.mem[pars[r][i]] = ("param", i % ws, -1, True)    # identical replicas, step -1
@@ -278,9 +291,13 @@ def drive_params(ws, nbuf, lanes, seed, drop_step_wait=False):
         main = ops.cur
         lane_streams = [main] + [SimStream(sim, f"r{r}.lane{i}") for i in range(1, lanes)]
         side = SimStream(sim, f"r{r}.side")
-        for step in range(2):
+        for step in range(steps):
+            if (r, step) in absent:      # this rank left before the step: it enqueues nothing more
+                break
             # the training loop reads the replicas before the step (all must be of step-1)
             def use(r=r, step=step):
+                if sim.relaxed:
+                    return
                 for i in range(nparams):
                     v = sim.mem[pars[r][i]]
                     assert v[2] == step - 1, f"rank {r} before step {step}: param {i} holds {v}"
@@ -319,7 +336,10 @@ def drive_params(ws, nbuf, lanes, seed, drop_step_wait=False):
                 for i in range(nparams):
                     v = sim.mem[pars[r][i]]
                     assert v[1] == i % ws and v[2] == step, f"rank {r} after step {step}: param {i} holds {v}"
-            main.push(lambda: True, check_end)
+            if not absent:
+                main.push(lambda: True, check_end)
+    if absent:
+        return sim, opses, gathers
     sim.run()
 
 
@@ -338,3 +358,87 @@ def _flush(sim, ops, pg, side, pars, r, nbytes, pending, upd_done, step):
     h.wait()
     h.done()
     upd_done[b] = ops.record(side)
+
+
+@pytest.mark.parametrize("ws,nbuf,lanes", [(2, 2, 1), (3, 4, 2), (4, 8, 4)])
+@pytest.mark.parametrize("seed", range(4))
+def test_a_rank_that_leaves_between_steps_is_detected_by_the_deadline(ws, nbuf, lanes, seed):
+    """Rank ws-1 takes part in step 0 and never enters step 1.  The streams of the others park on
+    flags nobody will write; past the deadline ``poll`` writes the awaited values itself, every
+    parked stream drains, the exchange is marked failed and the next step raises.  Before the
+    deadline nothing is touched."""
+    gone = ws - 1
+    sim, opses, gathers = drive_params(ws, nbuf, lanes, seed, absent={(gone, 1)}, timeout_s=30.0)
+    stuck = sim.run(allow_stuck=True)
+    assert stuck and not any(name.startswith(f"r{gone}.") for name in stuck)
+    live = [r for r in range(ws) if r != gone]
+    sim.clock = 29.0
+    for r in live:
+        assert gathers[r].poll() is True and gathers[r].failed is None
+    assert sim.run(allow_stuck=True) == stuck              # still parked, nothing released
+    sim.clock = 31.0
+    sim.relaxed = True                                     # released streams carry no valid data
+    for r in live:
+        assert gathers[r].poll() is False
+        assert "did not take part" in gathers[r].failed
+    assert sim.run(allow_stuck=True) == []                 # every stream drained
+    for r in live:
+        with pytest.raises(PeerExchangeError):
+            gathers[r].begin_step(opses[r].cur)
+    # the rank that left has nothing in flight and is not declared failed by its own deadline
+    assert gathers[gone].poll() is True
+
+
+def test_a_healthy_exchange_never_trips_the_deadline():
+    sim, opses, gathers = drive_params(3, 4, 2, 1, absent={(99, 99)}, timeout_s=5.0)
+    sim.clock = 1000.0                                      # long after: steps that finished do not count
+    assert sim.run(allow_stuck=True) == []
+    for g in gathers:
+        assert g.poll() is True and g.failed is None
+
+
+def test_a_producer_that_never_publishes_is_detected():
+    """Gather-of-updates exchange: rank 1 stops publishing after its second round (an exception in
+    its step).  Its peers wait for READY flags that never come; the deadline releases them."""
+    ws, nbuf, nbytes = 3, 2, 64
+    sim, opses, bufs, gathers = build_world(ws, nbuf, nbytes, seed=3, timeout_s=10.0)
+    for r in range(ws):
+        ops, pg = opses[r], gathers[r]
+        main, side = ops.cur, SimStream(sim, f"r{r}.side")
+        pg.begin_step(main)
+        pending = None
+
+        def consume(h, ops=ops, side=side, main=main, r=r):
+            ops.cur = side
+            h.wait()
+
+            def read(r=r, b=h.b):
+                for q in range(ws):
+                    a = bufs[r][b] + q * nbytes
+                    v = sim.mem.get(a)
+                    if v is not None:
+                        sim.mem[a] = (v[0], v[1], v[2], True)
+            side.push(lambda: True, read)
+            h.done()
+            ops.cur = main
+
+        for i in range(4):
+            if r == 1 and i == 2:
+                break                                       # rank 1 dies here
+            b = i % nbuf
+            ops.cur = main
+            pg.before_slot_write(0, b, main)
+            slot = bufs[r][b] + r * nbytes
+            main.push(lambda: True, lambda slot=slot, r=r, i=i: sim.mem.__setitem__(slot, ("slot", r, i, True)))
+            if pending is not None:
+                consume(pending)
+            pending = pg.publish(0, b, slot, nbytes, list(range(ws)))
+        if r != 1:
+            consume(pending)
+            ops.wait_event(main, ops.record(side))
+            pg.end_step(main)
+    assert sim.run(allow_stuck=True)
+    sim.clock = 11.0
+    sim.relaxed = True
+    assert gathers[0].poll() is False and gathers[2].poll() is False
+    assert [s for s in sim.run(allow_stuck=True) if not s.startswith("r1.")] == []

@@ -30,23 +30,30 @@ def _with_workspace(G, steps):
 
 
 def test_static_scratch_matches_workspace_entry_point_twice_in_a_row():
+    """Same kernels, same layout, other scratch: the outputs must be the workspace entry point's
+    bit for bit -- anything left over from the previous call in the shared array, a wrong region
+    offset or an overlap between regions would show up as a difference.  Calls go out on a
+    stream of their own, as a plugin would issue them."""
     torch.cuda.set_device(0)
     gen = torch.Generator(device=DEV).manual_seed(11)
-    first = torch.randn(1024, 4096, device=DEV, generator=gen).bfloat16()   # the largest allowed
-    second = torch.randn(520, 300, device=DEV, generator=gen)               # tall, f32, odd sizes
-    expected = [_with_workspace(first, 5), _with_workspace(second, 5)]
-    outs = [torch.empty_like(e) for e in expected]
+    inputs = [torch.randn(1024, 4096, device=DEV, generator=gen).bfloat16(),   # the largest allowed
+              torch.randn(520, 300, device=DEV, generator=gen),                # tall, f32, odd sizes
+              torch.randn(4096, 1024, device=DEV, generator=gen).bfloat16(),   # the largest, tall
+              torch.randn(1023, 4095, device=DEV, generator=gen).half()]       # off the grid, near the limit
+    expected = [_with_workspace(G, 5) for G in inputs]
+    outs = [torch.full_like(e, float("nan")) for e in expected]
+    stream = torch.cuda.Stream()
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
-    for G, out in zip((first, second), outs):                               # back to back
+    for G, out in zip(inputs, outs):                                           # back to back
         rows, cols = G.shape
         rc = lib.fm_newtonschulz_static(G.data_ptr(), rows, cols, cols, _lib.dtype_code(G.dtype), 5,
-                                        out.data_ptr(), 0, 0)
+                                        out.data_ptr(), 0, stream.cuda_stream)
         assert rc == 0, lib.fm_last_error()
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
     for out, exp in zip(outs, expected):
-        assert not torch.isnan(out).any()
+        assert torch.equal(out, exp)
         assert _rel(out, exp) <= 2e-2            # the tolerance of the Newton-Schulz parity tests
     _lib.device_status()
 
