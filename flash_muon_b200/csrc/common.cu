@@ -42,6 +42,7 @@ Options& options() {
     env("FM_GEMM_BALANCE", &opt.gemm_balance);
     env("FM_GEMM_STRIP", &opt.gemm_strip);
     env("FM_PDL", &opt.pdl);
+    env("FM_GEMM_TMA_STORE", &opt.gemm_tma_store);
   });
   return opt;
 }
@@ -56,6 +57,7 @@ int* option_slot(const char* name) {
   if (!strcmp(name, "gemm_balance")) return &o.gemm_balance;
   if (!strcmp(name, "gemm_strip")) return &o.gemm_strip;
   if (!strcmp(name, "pdl")) return &o.pdl;
+  if (!strcmp(name, "gemm_tma_store")) return &o.gemm_tma_store;
   return nullptr;
 }
 }  // namespace
@@ -99,7 +101,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 int encode_tmap_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
-                   uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer) {
+                   uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer, bool swizzle128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(FM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   CUtensorMapDataType dt;
@@ -116,7 +118,8 @@ int encode_tmap_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(FM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);

@@ -29,10 +29,10 @@ int sm_count();
 // Address of the device word kernels set when a bounded wait runs out.
 unsigned int* device_error_word();
 
-// Encodes a 2-D row-major tensor map (inner = contiguous dimension) with the 128-byte swizzle.
-// elem_bytes 2 only.  Returns FM_OK or an error status.
+// Encodes a 2-D row-major tensor map (inner = contiguous dimension) for 16-bit elements, with the
+// 128-byte swizzle (box rows of 128 bytes) or without any.  Returns FM_OK or an error status.
 int encode_tmap_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
-                   uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer);
+                   uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer, bool swizzle128 = true);
 
 // Process-wide tuning switches (fm_set_option / fm_get_option).  Initial values come from the
 // FM_GEMM_* / FM_PDL environment variables, read once when the library is first used; nothing on
@@ -44,6 +44,7 @@ struct Options {
   int gemm_balance = 1;  // 0: never cut the tail of a tile list by K blocks
   int gemm_strip = -1;   // symmetric lists of the pair kernel: -1 by size, 0 column order, w strips
   int pdl = 1;           // 0: launch the GEMM kernels without programmatic stream serialization
+  int gemm_tma_store = 1;  // 0: the pair kernel writes its outputs with per-lane global stores
 };
 Options& options();
 

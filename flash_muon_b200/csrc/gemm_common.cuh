@@ -45,6 +45,12 @@ struct GemmParams {
   long long d_batch, c_batch, t_batch;  // elements between consecutive problems in D, C, CT
   int use_c_tab;                        // 1: problem g writes its direct output to c_tab[g]
   void* c_tab[kMaxGemmBatch];
+  // CTA-pair kernel: outputs leave through shared-memory staging and TMA tile stores (full
+  // 64- and 128-byte row segments) instead of per-lane global stores.  Set by the host when every
+  // output is a 16-byte aligned, unit-column-stride matrix; tiles on the diagonal of a symmetric
+  // product keep the register path (their element-wise mirror rule).
+  int tma_store;
+  int c_batch_rows, t_batch_rows;       // rows between consecutive problems in the C / CT maps
 };
 
 // Base pointers of one problem of a (possibly batched) launch.
@@ -105,34 +111,14 @@ __device__ __forceinline__ void epilogue_load_d(const GemmParams& p, const EpiPt
   }
 }
 
-// One 32-column chunk of one accumulator row: arithmetic + stores.
-//   raw : fp32 accumulator bits of columns c0..c0+31 of `row`
-//   bi  : index of the 128-row block `row` belongs to (diagonal test of the symmetric product)
-// Symmetric mode: a 128-column block left of the diagonal block is skipped (its mirror image is
-// produced by the block above the diagonal); on the diagonal only c >= row is stored and
-// c > row mirrored, so both triangles come from the same rounded registers.
+// Arithmetic of one 32-column chunk of one accumulator row:
+//   raw : fp32 accumulator bits of columns c0..c0+31 of the row,  dv : the addend values
+//   out = round(round(alpha*D) + round(beta*round(acc)))  (one rounding with `precise`), or
+//   round(acc) without an addend.
 template <typename T>
-__device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiPtrs& e,
-                                               const uint32_t (&raw)[32], const T (&dv)[32], int row,
-                                               int c0, int bi) {
-  if (c0 >= p.N) return;  // warp-uniform
-  const int cb = c0 >> 7;
-  if (p.sym && cb < bi) return;  // warp-uniform
-  // Inside the diagonal 128 x 128 block the warp's 32 rows meet this chunk's 32 columns in one
-  // of three ways: wholly below the diagonal (nothing to store), wholly above (same as any
-  // other block) or on it (element-wise rule).  All three tests are warp-uniform.
-  bool diag = false;
-  if (p.sym && cb == bi) {
-    const int r_first = row & ~31;
-    if (c0 + 31 < r_first) return;
-    diag = (c0 < r_first + 32);
-  }
-  const bool full_cols = (c0 + 32 <= p.N);
-  const bool row_ok = row < p.M;
-  T* const Cp = reinterpret_cast<T*>(e.C);
-  T* const CTp = reinterpret_cast<T*>(e.CT);
-
-  alignas(16) T outv[32];
+__device__ __forceinline__ void epilogue_values(const GemmParams& p, const EpiPtrs& e,
+                                                const uint32_t (&raw)[32], const T (&dv)[32],
+                                                T (&outv)[32]) {
   if (e.D != nullptr) {
     if (p.precise) {
 #pragma unroll
@@ -151,6 +137,32 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiPtr
 #pragma unroll
     for (int j = 0; j < 32; ++j) outv[j] = Num<T>::rn(__uint_as_float(raw[j]));
   }
+}
+
+// Global stores of one chunk from registers (direct rows + transposed columns).
+//   bi  : index of the 128-row block `row` belongs to (diagonal test of the symmetric product)
+// Symmetric mode: a 128-column block left of the diagonal block is skipped (its mirror image is
+// produced by the block above the diagonal); on the diagonal only c >= row is stored and
+// c > row mirrored, so both triangles come from the same rounded registers.
+template <typename T>
+__device__ __forceinline__ void epilogue_store_regs(const GemmParams& p, const EpiPtrs& e,
+                                                    const T (&outv)[32], int row, int c0, int bi) {
+  if (c0 >= p.N) return;  // warp-uniform
+  const int cb = c0 >> 7;
+  if (p.sym && cb < bi) return;  // warp-uniform
+  // Inside the diagonal 128 x 128 block the warp's 32 rows meet this chunk's 32 columns in one
+  // of three ways: wholly below the diagonal (nothing to store), wholly above (same as any
+  // other block) or on it (element-wise rule).  All three tests are warp-uniform.
+  bool diag = false;
+  if (p.sym && cb == bi) {
+    const int r_first = row & ~31;
+    if (c0 + 31 < r_first) return;
+    diag = (c0 < r_first + 32);
+  }
+  const bool full_cols = (c0 + 32 <= p.N);
+  const bool row_ok = row < p.M;
+  T* const Cp = reinterpret_cast<T*>(e.C);
+  T* const CTp = reinterpret_cast<T*>(e.CT);
 
   if (Cp != nullptr && row_ok) {
     if (p.c_vec && full_cols && !diag) {
@@ -192,6 +204,48 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiPtr
         const int c = c0 + j;
         if (c < p.N && (!diag || c > row)) tptr[(long long)j * p.ldt_r] = outv[j];
       }
+    }
+  }
+}
+
+// Arithmetic + register stores of one chunk.
+template <typename T>
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiPtrs& e,
+                                               const uint32_t (&raw)[32], const T (&dv)[32], int row,
+                                               int c0, int bi) {
+  if (c0 >= p.N) return;  // warp-uniform
+  alignas(16) T outv[32];
+  epilogue_values<T>(p, e, raw, dv, outv);
+  epilogue_store_regs<T>(p, e, outv, row, c0, bi);
+}
+
+// Staging of one chunk for the TMA tile stores.  `lane` holds one row of the warp's 32 x 64
+// block (two chunks); half selects the chunk.
+//   sC : [32 rows][64 columns], rows of 128 bytes under the 128-byte swizzle (16-byte piece q of
+//        row r sits at piece q ^ (r & 7)), the layout a SWIZZLE_128B tensor map reads;
+//   sT : [64 columns][32 rows], rows of 64 bytes, no swizzle.
+// Both writes are free of bank conflicts: 8 consecutive lanes cover the 8 pieces of a 128-byte
+// span of sC, and the packed transposed words of one instruction fill 128 consecutive bytes of sT.
+template <typename T>
+__device__ __forceinline__ void epilogue_stage(const T (&outv)[32], uint8_t* sC, uint8_t* sT,
+                                               int lane, int half, bool want_c, bool want_t) {
+  if (want_c) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int piece = (half * 4 + v) ^ (lane & 7);
+      *reinterpret_cast<uint4*>(sC + lane * 128 + piece * 16) = reinterpret_cast<const uint4*>(outv)[v];
+    }
+  }
+  if (want_t) {
+    const uint32_t* own = reinterpret_cast<const uint32_t*>(outv);
+    const bool odd = (lane & 1) != 0;
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) {
+      const uint32_t mine = own[jj];
+      const uint32_t theirs = __shfl_xor_sync(0xffffffffu, mine, 1);
+      const uint32_t v = odd ? __byte_perm(theirs, mine, 0x7632) : __byte_perm(mine, theirs, 0x5410);
+      const int col = half * 32 + 2 * jj + (odd ? 1 : 0);
+      *reinterpret_cast<uint32_t*>(sT + col * 64 + (lane & ~1) * 2) = v;
     }
   }
 }

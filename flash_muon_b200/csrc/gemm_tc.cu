@@ -294,6 +294,8 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   }
   if (a.batch > 1 && p.use_c_tab && a.D && a.d_batch % 8 != 0) p.d_vec = 0;
   if (a.batch > 1 && p.use_c_tab && a.CT && a.t_batch % 2 != 0) p.t_pack = 0;
+  p.tma_store = 0;
+  p.c_batch_rows = p.t_batch_rows = 0;
   p.err = device_error_word();
   if (!p.err) return fail(FM_ERR_CUDA, "no current CUDA device");
 
@@ -312,7 +314,38 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
       impl = 2;
     }
   }
-  if (impl == 2) return gemm_tc2_launch(a.dtype, tmA, tmB, p, a.sk_ws, a.sk_bytes, stream);
+  if (impl == 2) {
+    // Outputs through TMA tile stores when every output is a matrix TMA can address: unit column
+    // stride, 16-byte aligned base and pitch, one base for the whole batch, and (batch > 1) no
+    // tile hanging over the edge of a problem into the rows of the next one.
+    auto addressable = [](const void* ptr, int64_t ld_r, int64_t ld_c) {
+      return ptr == nullptr || (ld_c == 1 && ld_r % 8 == 0 && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0);
+    };
+    CUtensorMap tmC = tmA, tmT = tmA;  // placeholders unless the stores use them
+    p.tma_store = 0;
+    p.c_batch_rows = p.t_batch_rows = 0;
+    bool ok = options().gemm_tma_store && !p.use_c_tab && addressable(a.C, a.ldc_r, a.ldc_c) &&
+              addressable(a.CT, a.ldt_r, a.ldt_c);
+    if (ok && a.batch > 1) {
+      ok = (a.M % 256 == 0) && (a.N % 256 == 0) && (!a.C || a.c_batch % a.ldc_r == 0) &&
+           (!a.CT || a.t_batch % a.ldt_r == 0);
+      if (ok) {
+        p.c_batch_rows = a.C ? (int)(a.c_batch / a.ldc_r) : 0;
+        p.t_batch_rows = a.CT ? (int)(a.t_batch / a.ldt_r) : 0;
+      }
+    }
+    if (ok && a.C)
+      ok = encode_tmap_2d(&tmC, a.dtype, a.C, (uint64_t)a.N,
+                          (uint64_t)(a.batch - 1) * (uint64_t)p.c_batch_rows + (uint64_t)a.M,
+                          (uint64_t)a.ldc_r, 64, 32, true) == FM_OK;
+    if (ok && a.CT)
+      ok = encode_tmap_2d(&tmT, a.dtype, a.CT, (uint64_t)a.M,
+                          (uint64_t)(a.batch - 1) * (uint64_t)p.t_batch_rows + (uint64_t)a.N,
+                          (uint64_t)a.ldt_r, 32, 64, false) == FM_OK;
+    clear_error();
+    p.tma_store = ok ? 1 : 0;
+    return gemm_tc2_launch(a.dtype, tmA, tmB, tmC, tmT, p, a.sk_ws, a.sk_bytes, stream);
+  }
 
   // Tile width: 256 columns (less operand traffic per FLOP) unless that leaves most SMs idle.
   int bn = 256;

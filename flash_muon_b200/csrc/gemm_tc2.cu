@@ -16,6 +16,13 @@
 // so that many small matrices share one launch -- the grouped form Newton-Schulz uses for
 // matrices too small to fill the GPU on their own.
 //
+// Outputs leave through shared memory: each epilogue warp converts its 32 rows x 64 columns,
+// writes them row-wise and transposed into two small staging tiles and lets TMA store both (full
+// 128- and 64-byte row segments; rows and columns past the matrix edge are clipped by the tensor
+// map).  Per-lane global stores (32 scattered 16-byte pieces per instruction) cost 14-23 % of a
+// K = 4096 product although they overlap the main loop; tiles on the diagonal of a symmetric
+// product, with their element-wise mirror rule, and outputs TMA cannot address keep that path.
+//
 // The kernel is launched with programmatic stream serialization: its set-up (barriers, TMEM,
 // tensor-map prefetch) runs while the previous kernel of the stream drains, and every CTA lets
 // the next kernel be scheduled when it starts its last piece of work.
@@ -40,7 +47,12 @@ constexpr int kDefaultStages = 6;
 constexpr int kStageBytes = 2 * kSlabBytes;   // this CTA's A slab + B slab
 constexpr int kTmemCols = 512;                // two accumulators of 256 fp32 columns
 constexpr int kNumBars = 2 * kMaxStages + 4;
-constexpr int smem_bytes(int stages) { return stages * kStageBytes + kNumBars * 8 + 16 + 1024; }
+// staging of the TMA stores: per epilogue warp 32 x 64 values row-wise (4 KiB) and transposed (4 KiB)
+constexpr int kStagingBytes = 4 * 8192;
+constexpr int kMaxStagesWithStaging = 6;
+constexpr int smem_bytes(int stages, bool staging) {
+  return stages * kStageBytes + (staging ? kStagingBytes : 0) + kNumBars * 8 + 16 + 1024;
+}
 
 // Scratch of the balanced tail: deposit counters first, then one partial accumulator per CTA of
 // every pair (128 rows x 256 fp32 columns each: a pair leaves at most one tile unfinished).
@@ -66,14 +78,17 @@ __device__ __forceinline__ TileRef locate(const GemmParams& p, int t) {
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmT,
                 const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const int kStages = p.stages;  // ring depth chosen by the host
   const uint32_t smem_base = ptx::smem_u32(smem);
-  const uint32_t bar_base = smem_base + kStages * kStageBytes;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kStages * kStageBytes + kNumBars * 8);
+  const int staging_off = kStages * kStageBytes;  // multiple of 1024: the swizzled tile needs it
+  const int bar_off = staging_off + (p.tma_store ? kStagingBytes : 0);
+  const uint32_t bar_base = smem_base + bar_off;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + bar_off + kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -102,6 +117,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&tmA);
     ptx::prefetch_tmap(&tmB);
+    if (p.tma_store) {
+      if (p.C != nullptr) ptx::prefetch_tmap(&tmC);
+      if (p.CT != nullptr) ptx::prefetch_tmap(&tmT);
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
@@ -191,6 +210,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     int acc = 0;
     uint32_t acc_ph = 0;
     volatile int* sk_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    uint8_t* const sC = smem + staging_off + q * 8192;  // this warp's staging tiles
+    uint8_t* const sT = sC + 4096;
     WorkIter it(p, pair, npairs);
     WorkItem w;
     while (it.next(p, w)) {
@@ -199,7 +220,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const EpiPtrs ep = epilogue_ptrs(p, tr.g, (int)sizeof(T));
       const int row_local = q * 32 + lane;
       const int row = tl.m0 + (int)rank * 128 + row_local;
+      const int row0w = row - lane;               // first row of this warp's 32
       const int bi = (tl.m0 >> 7) + (int)rank;
+      // tile stores for everything but the diagonal tiles of a symmetric product
+      const bool tma_tile = p.tma_store && !(p.sym && tl.m0 == tl.n0);
       alignas(16) T dcur[32], dnext[32];
       if (!w.deposit) epilogue_load_d<T>(p, ep, row, tl.n0, dcur);
 
@@ -269,7 +293,33 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
             for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(psum[j] + __uint_as_float(raw[j]));
           }
-          epilogue_store<T>(p, ep, raw, dcur, row, tl.n0 + ch * 32, bi);
+          const int c0 = tl.n0 + ch * 32;
+          if (!tma_tile) {
+            epilogue_store<T>(p, ep, raw, dcur, row, c0, bi);
+          } else if (row0w < p.M && (c0 & ~63) < p.N) {  // warp-uniform: something of this 64-column pair is inside
+            const int half = ch & 1;
+            if (c0 < p.N) {
+              alignas(16) T outv[32];
+              epilogue_values<T>(p, ep, raw, dcur, outv);
+              if (half == 0) {  // the previous stores of this warp have let go of the staging tiles
+                if (lane == 0) ptx::bulk_wait_read_all();
+                __syncwarp();
+              }
+              epilogue_stage<T>(outv, sC, sT, lane, half, ep.C != nullptr, ep.CT != nullptr);
+            }
+            if (half == 1) {
+              ptx::fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                const int cx = c0 - 32;  // first column of the pair
+                if (ep.C != nullptr)
+                  ptx::tma_store_2d(&tmC, ptx::smem_u32(sC), cx, tr.g * p.c_batch_rows + row0w);
+                if (ep.CT != nullptr)
+                  ptx::tma_store_2d(&tmT, ptx::smem_u32(sT), row0w, tr.g * p.t_batch_rows + cx);
+                ptx::bulk_commit();
+              }
+            }
+          }
           if (ep.D != nullptr) {
 #pragma unroll
             for (int v = 0; v < 4; ++v)
@@ -308,6 +358,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (threadIdx.x == 64) atomicAdd(p.sk_cnt + (w.sk_tile * 2 + (int)rank), 1u);
       }
     }
+    // tile stores in flight read this CTA's shared memory and must be performed before the grid
+    // counts as complete for its dependents
+    if (p.tma_store && lane == 0) ptx::bulk_wait_all();
+    __syncwarp();
   }
 
   // ---------------------------------------------------------------- teardown
@@ -325,9 +379,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 // Ring depth: 6 stages of 32 KiB by default; 4 cost 2-3 % on the large products, 3 cost 12 %.
-int pair_stages() {
+int pair_stages(bool staging) {
   const int w = options().gemm_stages;
-  return (w >= 2 && w <= kMaxStages) ? w : kDefaultStages;
+  const int v = (w >= 2 && w <= kMaxStages) ? w : kDefaultStages;
+  return (staging && v > kMaxStagesWithStaging) ? kMaxStagesWithStaging : v;
 }
 
 // Tile order of a symmetric list: column strips of width w (tile_schedule.cuh has the reasoning:
@@ -347,13 +402,16 @@ int max_pairs_for() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
   if (cached[dev] == 0) {
+    constexpr int kMost = smem_bytes(kMaxStages, false) > smem_bytes(kMaxStagesWithStaging, true)
+                              ? smem_bytes(kMaxStages, false)
+                              : smem_bytes(kMaxStagesWithStaging, true);
     if (cudaFuncSetAttribute(gemm_tc2_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem_bytes(kMaxStages)) != cudaSuccess)
+                             kMost) != cudaSuccess)
       return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2);
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem_bytes(kDefaultStages);
+    cfg.dynamicSmemBytes = smem_bytes(kDefaultStages, true);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
@@ -381,8 +439,9 @@ bool balance_plan(int tiles, int num_kb, int max_pairs, int batch, int* dp_tiles
 }
 
 template <typename T>
-int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int max_pairs,
-            void* sk_ws, size_t sk_bytes, cudaStream_t stream) {
+int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+            const CUtensorMap& tmT, GemmParams& p, int max_pairs, void* sk_ws, size_t sk_bytes,
+            cudaStream_t stream) {
   const int T_all = p.num_tiles;
   int pairs = T_all < max_pairs ? T_all : max_pairs;
   p.sk_dp_tiles = T_all;
@@ -404,11 +463,11 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int m
     // the deposit counters start every launch at zero, whatever an earlier launch left behind
     FM_CUDA_CHECK(cudaMemsetAsync(p.sk_cnt, 0, kSkCntBytes, stream));
   }
-  p.stages = pair_stages();
+  p.stages = pair_stages(p.tma_store != 0);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem_bytes(p.stages);
+  cfg.dynamicSmemBytes = smem_bytes(p.stages, p.tma_store != 0);
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -422,7 +481,7 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int m
     cfg.numAttrs = 2;
   }
   cfg.attrs = attr;
-  FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T>, tmA, tmB, p));
+  FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T>, tmA, tmB, tmC, tmT, p));
   return FM_OK;
 }
 
@@ -447,16 +506,18 @@ size_t gemm_tc2_sk_bytes(int dtype, int64_t M, int64_t N, int64_t K, int sym) {
 }
 
 // `p` arrives filled except for the schedule fields, which depend on the tile shape.
-int gemm_tc2_launch(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
-                    void* sk_ws, size_t sk_bytes, cudaStream_t stream) {
+int gemm_tc2_launch(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                    const CUtensorMap& tmC, const CUtensorMap& tmT, GemmParams& p, void* sk_ws,
+                    size_t sk_bytes, cudaStream_t stream) {
   p.tiles_m = (p.M + 255) / 256;
   p.tiles_per_batch = gemm_tc2_tiles(p.M, p.N, p.sym);
   p.num_tiles = p.tiles_per_batch * p.batch;
   p.strip_w = strip_width(p);
   const int max_pairs = gemm_tc2_max_pairs(dtype);
   if (max_pairs <= 0) return fail(FM_ERR_CUDA, "no resident CTA pair possible for the GEMM kernel");
-  return dtype == FM_BF16 ? launch2<__nv_bfloat16>(tmA, tmB, p, max_pairs, sk_ws, sk_bytes, stream)
-                          : launch2<__half>(tmA, tmB, p, max_pairs, sk_ws, sk_bytes, stream);
+  return dtype == FM_BF16
+             ? launch2<__nv_bfloat16>(tmA, tmB, tmC, tmT, p, max_pairs, sk_ws, sk_bytes, stream)
+             : launch2<__half>(tmA, tmB, tmC, tmT, p, max_pairs, sk_ws, sk_bytes, stream);
 }
 
 }  // namespace fm
