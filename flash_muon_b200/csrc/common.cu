@@ -43,6 +43,9 @@ Options& options() {
     env("FM_GEMM_STRIP", &opt.gemm_strip);
     env("FM_PDL", &opt.pdl);
     env("FM_GEMM_TMA_STORE", &opt.gemm_tma_store);
+    env("FM_GEMM_KB_PER_STAGE", &opt.gemm_kb_per_stage);
+    env("FM_PDL_TRIGGER", &opt.pdl_trigger);
+    env("FM_GEMM_L2_PROMOTION", &opt.gemm_l2_promotion);
   });
   return opt;
 }
@@ -58,6 +61,9 @@ int* option_slot(const char* name) {
   if (!strcmp(name, "gemm_strip")) return &o.gemm_strip;
   if (!strcmp(name, "pdl")) return &o.pdl;
   if (!strcmp(name, "gemm_tma_store")) return &o.gemm_tma_store;
+  if (!strcmp(name, "gemm_kb_per_stage")) return &o.gemm_kb_per_stage;
+  if (!strcmp(name, "pdl_trigger")) return &o.pdl_trigger;
+  if (!strcmp(name, "gemm_l2_promotion")) return &o.gemm_l2_promotion;
   return nullptr;
 }
 }  // namespace
@@ -120,7 +126,11 @@ int encode_tmap_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner
   CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  options().gemm_l2_promotion == 0   ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                  : options().gemm_l2_promotion == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                  : options().gemm_l2_promotion == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                     : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(FM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return FM_OK;

@@ -44,6 +44,9 @@ struct Options {
   int gemm_balance = 1;  // 0: never cut the tail of a tile list by K blocks
   int gemm_strip = -1;   // symmetric lists of the pair kernel: -1 by size, 0 column order, w strips
   int pdl = 1;           // 0: launch the GEMM kernels without programmatic stream serialization
+  int gemm_l2_promotion = 3;  // L2 promotion of the tensor maps: 0 none, 1 64 B, 2 128 B, 3 256 B
+  int pdl_trigger = 0;   // when CTAs release the next kernel: 0 by schedule, 1 always early, 2 never
+  int gemm_kb_per_stage = 2;  // pair kernel: 64-wide K blocks per pipeline stage (1..3)
   int gemm_tma_store = 1;  // 0: the pair kernel writes its outputs with per-lane global stores
 };
 Options& options();

@@ -28,7 +28,9 @@ struct GemmParams {
   int d_vec;      // D rows can be read with 16-byte loads
   int c_vec;      // C rows can be written with 16-byte stores
   int t_pack;     // CT can be written as pairs of adjacent rows (4-byte stores)
-  int stages;     // depth of the shared-memory ring (CTA-pair kernel)
+  int stages;     // slots (64-wide K blocks) of the shared-memory ring (CTA-pair kernel)
+  int kb_per_stage;  // K blocks per pipeline stage (1 or 2)
+  int early_trigger; // 1: CTAs release the next kernel of the stream when they start their last item
   // balanced tail of the CTA-pair kernel (all zero: every tile is dealt whole)
   int sk_dp_tiles;         // tiles dealt whole, round-robin; the rest is cut by K blocks
   int sk_per;              // K blocks per pair in the balanced region

@@ -273,6 +273,8 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   p.t_pack = (a.CT != nullptr) && (a.ldt_c == 1) && (a.ldt_r % 2 == 0) &&
              ((reinterpret_cast<uintptr_t>(a.CT) & 3u) == 0);
   p.stages = 0;
+  p.kb_per_stage = 1;
+  p.early_trigger = 1;
   p.strip_w = 0;
   p.sk_dp_tiles = 0; p.sk_per = 0; p.sk_total = 0; p.sk_ws = nullptr; p.sk_cnt = nullptr;
   p.batch = a.batch;

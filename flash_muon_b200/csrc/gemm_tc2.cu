@@ -24,8 +24,11 @@
 // product, with their element-wise mirror rule, and outputs TMA cannot address keep that path.
 //
 // The kernel is launched with programmatic stream serialization: its set-up (barriers, TMEM,
-// tensor-map prefetch) runs while the previous kernel of the stream drains, and every CTA lets
-// the next kernel be scheduled when it starts its last piece of work.
+// tensor-map prefetch) runs while the previous kernel of the stream drains.  A launch whose CTAs
+// all finish together (one wave, or a balanced tail) lets the next kernel be placed as soon as
+// every CTA has started its last piece of work; a launch with a ragged last wave does not, because
+// SMs that fall idle early are better taken by a kernel of another stream than by a successor
+// that can only wait.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -83,9 +86,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  const int kStages = p.stages;  // ring depth chosen by the host
+  // The ring has p.stages slots of one 64-wide K block each; a pipeline stage (one full / empty
+  // barrier pair) covers p.kb_per_stage consecutive slots.
+  const int kbs = p.kb_per_stage;
+  const int kStages = p.stages / kbs;
   const uint32_t smem_base = ptx::smem_u32(smem);
-  const int staging_off = kStages * kStageBytes;  // multiple of 1024: the swizzled tile needs it
+  const int staging_off = p.stages * kStageBytes;  // multiple of 1024: the swizzled tile needs it
   const int bar_off = staging_off + (p.tma_store ? kStagingBytes : 0);
   const uint32_t bar_base = smem_base + bar_off;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + bar_off + kNumBars * 8);
@@ -137,17 +143,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer (both CTAs)
-    if (lane == 0) {
+    // Like the MMA issuer, the whole warp runs the loop convergently and only the TMA and
+    // barrier instructions are predicated on the leading lane.
+    {
+      const uint32_t lead = (lane == 0) ? 1u : 0u;
+      const uint32_t expect_lead = (lane == 0 && rank == 0) ? 1u : 0u;
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
       WorkIter it(p, pair, npairs);
       WorkItem w, nxt;
       bool have = it.next(p, w);
-      if (!have) ptx::grid_dep_launch();
+      if (!have && p.early_trigger && lane == 0) ptx::grid_dep_launch();
       while (ok && have) {
         const bool more = it.next(p, nxt);
-        if (!more) ptx::grid_dep_launch();  // last piece of work of this CTA: the next kernel may be placed
+        // last piece of work of this CTA: the next kernel of the stream may be placed
+        if (!more && p.early_trigger && lane == 0) ptx::grid_dep_launch();
         const TileRef tr = locate(p, w.tile);
         const Tile2 tl = tr.tl;
         const int ya = tr.g * p.a_batch_rows + tl.m0 + (int)rank * 128;
@@ -155,12 +166,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // On a diagonal tile of the symmetric product the B slab is the A slab (same rows of
         // the same matrix): load it once and let the MMA read it through both descriptors.
         const bool same = p.sym && (tl.m0 == tl.n0);
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+        const uint32_t load_b = same ? 0u : lead;
+        for (int kb = w.kb0; kb < w.kb1; kb += kbs) {
+          const int nh = (w.kb1 - kb) < kbs ? (w.kb1 - kb) : kbs;  // K blocks of this stage
           if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t leader_full = ptx::mapa(full_bar(s), 0);
-          if (rank == 0) ptx::mbar_expect_tx(full_bar(s), (same ? 2u : 4u) * kSlabBytes);
-          ptx::tma_load_2d_pair(a_smem(s), &tmA, leader_full, kb * BK, ya);
-          if (!same) ptx::tma_load_2d_pair(b_smem(s), &tmB, leader_full, kb * BK, yb);
+          ptx::mbar_expect_tx_lead(full_bar(s), (uint32_t)nh * (same ? 2u : 4u) * kSlabBytes, expect_lead);
+          for (int h = 0; h < nh; ++h) {
+            ptx::tma_load_2d_pair_lead(a_smem(s * kbs + h), &tmA, leader_full, (kb + h) * BK, ya, lead);
+            ptx::tma_load_2d_pair_lead(b_smem(s * kbs + h), &tmB, leader_full, (kb + h) * BK, yb, load_b);
+          }
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
         w = nxt;
@@ -169,14 +184,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer (leader only)
-    if (lane == 0 && rank == 0) {
+    // ------------------------------------------------------------- MMA issuer (leader CTA only)
+    // The tensor pipe holds only a few MMAs, so the issuing code is on the critical path:
+    // whatever runs between two MMAs (barrier poll, descriptor arithmetic, commit) has to fit
+    // under the ones still queued.  The whole warp runs the loop convergently -- addresses and
+    // descriptors then stay warp-uniform values -- and only the MMA and commit instructions
+    // themselves are predicated on the leading lane; the MMAs of a stage are straight-line code,
+    // and the wait for the NEXT stage's data sits in front of the last MMA of the current one.
+    if (rank == 0) {
+      const uint32_t lead = (lane == 0) ? 1u : 0u;
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
       const uint32_t idesc = ptx::make_idesc_f16(Num<T>::kFormat, 256, 256);
+      const uint64_t desc_base = ptx::make_kmajor_sw128_desc(a_smem(0));  // slot 0, A slab
+      constexpr uint32_t kSlotStep = (uint32_t)(kStageBytes >> 4);        // descriptor units per slot
       WorkIter it(p, pair, npairs);
       WorkItem w;
       while (ok && it.next(p, w)) {
@@ -185,20 +209,48 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
         const Tile2 tl = locate(p, w.tile).tl;
         const bool same = p.sym && (tl.m0 == tl.n0);
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
-          ptx::tc_fence_after();
-          const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_smem(s));
-          const uint64_t b_desc = same ? a_desc : ptx::make_kmajor_sw128_desc(b_smem(s));
+        int kb = w.kb0;
+        if (kb < w.kb1 && !ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+        while (kb < w.kb1) {
+          const int nh = (w.kb1 - kb) < kbs ? (w.kb1 - kb) : kbs;
+          const int s_next = (s + 1 == kStages) ? 0 : s + 1;
+          const uint32_t ph_next = (s + 1 == kStages) ? (ph ^ 1u) : ph;
+          const bool more = kb + nh < w.kb1;
+          const uint64_t a0 = desc_base + (uint64_t)((uint32_t)(s * kbs) * kSlotStep);
+          const uint64_t b0 = same ? a0 : a0 + (uint64_t)(kSlabBytes >> 4);
+          const uint32_t first = (kb != w.kb0) ? 1u : 0u;
+          // MMA i of a stage reads K block i / 4 (one slot further on per block) and the 16
+          // columns i % 4 of it (32 bytes = 2 in the descriptor's address field)
+          if (nh == 1) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            ptx::umma_f16_pair(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
-                               (uint32_t)((kb != w.kb0) || (k != 0)));
-          ptx::umma_commit_pair(empty_bar(s), 0x3);  // frees the stage in both CTAs
-          if (++s == kStages) { s = 0; ph ^= 1u; }
+            for (int i = 0; i < 4; ++i) {
+              if (i == 3 && more && !ptx::mbar_wait(full_bar(s_next), ph_next, abort_flag)) ok = false;
+              ptx::umma_f16_pair_lead(d_tmem, a0 + (uint64_t)(2 * i), b0 + (uint64_t)(2 * i), idesc,
+                                      i == 0 ? first : 1u, lead);
+            }
+          } else if (nh == 2) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (i == 7 && more && !ptx::mbar_wait(full_bar(s_next), ph_next, abort_flag)) ok = false;
+              const uint64_t off = (uint64_t)((i >> 2) * kSlotStep + (i & 3) * 2);
+              ptx::umma_f16_pair_lead(d_tmem, a0 + off, b0 + off, idesc, i == 0 ? first : 1u, lead);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 12; ++i) {
+              if (i == 11 && more && !ptx::mbar_wait(full_bar(s_next), ph_next, abort_flag)) ok = false;
+              const uint64_t off = (uint64_t)((i >> 2) * kSlotStep + (i & 3) * 2);
+              ptx::umma_f16_pair_lead(d_tmem, a0 + off, b0 + off, idesc, i == 0 ? first : 1u, lead);
+            }
+          }
+          ptx::umma_commit_pair_lead(empty_bar(s), 0x3, lead);  // frees the stage in both CTAs
+          if (!ok) break;
+          kb += nh;
+          s = s_next;
+          ph = ph_next;
         }
         if (!ok) break;
-        ptx::umma_commit_pair(tfull_bar(acc), 0x3);  // accumulator halves complete in both CTAs
+        ptx::umma_commit_pair_lead(tfull_bar(acc), 0x3, lead);  // accumulator halves complete in both CTAs
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
       }
@@ -463,7 +515,16 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& t
     // the deposit counters start every launch at zero, whatever an earlier launch left behind
     FM_CUDA_CHECK(cudaMemsetAsync(p.sk_cnt, 0, kSkCntBytes, stream));
   }
+  {
+    const int mode = options().pdl_trigger;  // 0 by schedule, 1 always early, 2 never
+    p.early_trigger = mode == 1 || (mode == 0 && (T_all <= max_pairs || p.sk_per > 0));
+  }
   p.stages = pair_stages(p.tma_store != 0);
+  {
+    const int want = options().gemm_kb_per_stage;
+    p.kb_per_stage = (want >= 1 && want <= 3 && p.stages / want >= 2) ? want : 1;
+  }
+  p.stages -= p.stages % p.kb_per_stage;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   cfg.blockDim = dim3(kThreads);

@@ -285,6 +285,58 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, 
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Tile load and byte-count announcement for a warp that runs its producer loop convergently: all
+// lanes execute the surrounding code, the instruction is predicated on `lead` (one lane).
+__device__ __forceinline__ void tma_load_2d_pair_lead(uint32_t dst_smem, const void* tmap,
+                                                      uint32_t bar_cluster_addr, int32_t x, int32_t y,
+                                                      uint32_t lead) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];\n\t"
+      "}\n"
+      ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y),
+        "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_lead(uint32_t bar, uint32_t bytes, uint32_t lead) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t"
+      "}\n" ::"r"(bar), "r"(bytes), "r"(lead)
+      : "memory");
+}
+
+// The same MMA and commit for a warp that runs its issuing loop convergently: every lane executes
+// the surrounding code (so that addresses and descriptors stay warp-uniform values), the
+// instruction itself is predicated on `lead`, which is non-zero in exactly one lane.
+__device__ __forceinline__ void umma_f16_pair_lead(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                   uint32_t idesc, uint32_t accumulate, uint32_t lead) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair_lead(uint32_t bar, uint16_t cta_mask, uint32_t lead) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;\n\t"
+      "}\n" ::"r"(bar),
+      "h"(cta_mask), "r"(lead)
+      : "memory");
+}
 // One arrival on the mbarrier at the same shared-memory offset in every CTA of `cta_mask`, once
 // all MMAs issued so far by this thread are done.  (A commit, not a load.)
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {

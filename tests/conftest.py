@@ -45,6 +45,29 @@ def options():
         _lib.set_option(name, value)
 
 
+_OBSERVED: dict = {}
+
+
+def observe(name: str, value: float) -> float:
+    """Remembers a measured distance under ``name`` (largest value wins) and returns it; at the end
+    of a GPU session everything observed is written to ``gpurun_out/parity_observed.json``, the
+    record the tolerances in these tests are set from."""
+    _OBSERVED[name] = max(float(value), _OBSERVED.get(name, 0.0))
+    return value
+
+
+def pytest_sessionfinish(session, exitstatus):
+    if not _OBSERVED:
+        return
+    import json
+    try:
+        out = ROOT / "gpurun_out"
+        out.mkdir(exist_ok=True)
+        (out / "parity_observed.json").write_text(json.dumps(dict(sorted(_OBSERVED.items())), indent=1))
+    except OSError:
+        pass
+
+
 def rel_fro(a: torch.Tensor, b: torch.Tensor) -> float:
     """||a - b||_F / ||b||_F in float64."""
     a = a.detach().double().cpu()

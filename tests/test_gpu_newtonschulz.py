@@ -5,7 +5,7 @@ import torch
 
 import flash_muon_b200 as fm
 from flash_muon_b200 import _lib
-from conftest import rel_fro
+from conftest import observe, rel_fro
 from inputs import NS_SHAPES, ns_input
 from oracle import muon_oracle as O
 
@@ -43,8 +43,8 @@ def test_golden_cases(golden, shape, steps):
     # tiny matrices sit on a higher bf16 noise floor than the 4096^2 config the 2e-2 bar is set
     # on: the reference's own two formulations differ by 3.5e-2 here (see test_oracle_golden)
     tol = TOL_STEPS[steps] if steps < 5 else 4e-2
-    assert rel_fro(out, ref) <= tol
-    assert rel_fro(out, torch_cuda_ns(G.to(DEV), steps)) <= 2e-3
+    assert observe(f"ns_golden/{shape[0]}x{shape[1]}/steps{steps}/vs_reference_cpu", rel_fro(out, ref)) <= tol
+    assert observe(f"ns_golden/steps{steps}/vs_torch_cuda", rel_fro(out, torch_cuda_ns(G.to(DEV), steps))) <= 2e-3
     _lib.device_status()
 
 
@@ -53,12 +53,13 @@ def test_config1_4096_bf16_5_steps():
     G = torch.randn(4096, 4096, generator=torch.Generator().manual_seed(0))
     out = fm.fast_newtonschulz(G.to(DEV).bfloat16(), 5)
     ref_cpu = O.newtonschulz(G.bfloat16(), 5)
-    err = rel_fro(out, ref_cpu)
+    err = observe("ns_config1_4096/steps5/vs_cpu_oracle", rel_fro(out, ref_cpu))
     assert err <= 2e-2, err
-    assert rel_fro(out, torch_cuda_ns(G.to(DEV).bfloat16(), 5)) <= 2e-3
+    assert observe("ns_config1_4096/steps5/vs_torch_cuda", rel_fro(out, torch_cuda_ns(G.to(DEV).bfloat16(), 5))) <= 2e-3
     # per-step errors against the oracle, for the record of how the difference grows
     for s in (1, 3):
-        assert rel_fro(fm.fast_newtonschulz(G.to(DEV), s), O.newtonschulz(G, s)) <= TOL_STEPS[s]
+        assert observe(f"ns_config1_4096/steps{s}/vs_cpu_oracle",
+                       rel_fro(fm.fast_newtonschulz(G.to(DEV), s), O.newtonschulz(G, s))) <= TOL_STEPS[s]
     _lib.device_status()
 
 
@@ -77,7 +78,8 @@ def test_shapes_and_dtypes_against_torch_cuda(shape, dt):
         # cuBLAS picks other kernels (another order of the fp32 sums) for sizes off its tile
         # grid; on small matrices that alone moves a 5-step bf16 iterate by 2-3e-2
         tol = 2e-2 if min(shape) >= 1024 else 4e-2
-        assert rel_fro(out, ref) <= tol, (shape, dt, steps)
+        cls = "wide1024" if min(shape) >= 1024 else "small"
+        assert observe(f"ns_shapes/{cls}/steps{steps}/vs_torch_cuda", rel_fro(out, ref)) <= tol, (shape, dt, steps)
     _lib.device_status()
 
 
@@ -85,7 +87,8 @@ def test_shapes_and_dtypes_against_torch_cuda(shape, dt):
 def test_against_cpu_oracle(shape):
     G = torch.randn(*shape, generator=torch.Generator().manual_seed(shape[0] + 3 * shape[1]))
     out = fm.fast_newtonschulz(G.to(DEV), 5)
-    assert rel_fro(out, O.newtonschulz(G, 5)) <= 2.5e-2  # 1024-wide shapes: noise floor ~1.8e-2
+    # 1024-wide shapes: noise floor ~1.8e-2
+    assert observe(f"ns_cpu_oracle/{shape[0]}x{shape[1]}/steps5", rel_fro(out, O.newtonschulz(G, 5))) <= 2.5e-2
 
 
 @pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (4096, 14336), (14336, 4096)])
@@ -101,7 +104,7 @@ def test_full_size_properties(shape):
     # a square Gaussian matrix has singular values down to ~0, which five steps cannot lift;
     # the bulk must still have been pushed into the band
     assert (sv > 0.5).double().mean() > (0.97 if shape[0] != shape[1] else 0.85), sv.min().item()
-    assert rel_fro(out, torch_cuda_ns(G, 5)) <= 2e-2
+    assert observe("ns_full_size/steps5/vs_torch_cuda", rel_fro(out, torch_cuda_ns(G, 5))) <= 2e-2
     assert torch.equal(out, fm.fast_newtonschulz(G, 5)), "run-to-run determinism"
     _lib.device_status()
 
