@@ -44,6 +44,7 @@ sys.path.insert(0, str(ROOT))
 LLAMA_LAYER = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (14336, 4096),
                (4096, 14336)]  # q k v o gate up down
 N_LAYERS = 32
+GPT2_LAYER = [(1024, 1024)] * 4 + [(4096, 1024), (1024, 4096)]  # configs[3]: 24 such layers
 HP = dict(lr=0.02, weight_decay=0.01, momentum=0.95, nesterov=True, ns_steps=5)
 SYRK_DIM = 8192
 
@@ -401,7 +402,7 @@ def run_ours(args):
         print(json.dumps({"matmul_transpose": mt, "roofline": roof}), flush=True)
         return
 
-    shapes = LLAMA_LAYER * args.layers
+    shapes = (GPT2_LAYER if args.workload == "gpt2" else LLAMA_LAYER) * args.layers
     g = torch.Generator(device=dev).manual_seed(0)  # same values on every rank (DP replicas)
     params = [torch.nn.Parameter((torch.randn(*s, device=dev, generator=g) * 0.02).bfloat16())
               for s in shapes]
@@ -577,7 +578,7 @@ def run_ours(args):
         # {4 x [1024,1024], [4096,1024], [1024,4096]}, same hyper-parameters, one GPU
         del params, opt, owned, owned_set
         torch.cuda.empty_cache()
-        gshapes = ([(1024, 1024)] * 4 + [(4096, 1024), (1024, 4096)]) * 24
+        gshapes = GPT2_LAYER * 24
         gp = [torch.nn.Parameter((torch.randn(*s, device=dev, generator=g) * 0.02).bfloat16())
               for s in gshapes]
         for p in gp:
@@ -624,6 +625,8 @@ def main():
     # profiling aids (the defaults are the benchmark):
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers of the matrix set (32 = the config)")
     ap.add_argument("--skip-extras", action="store_true", help="device-resident leg only")
+    ap.add_argument("--workload", default="llama", choices=["llama", "gpt2"],
+                    help="with --skip-extras: matrix set of the profiled step (gpt2 = configs[3], use --layers 24)")
     ap.add_argument("--syrk-only", action="store_true", help="only the matmul_transpose leg")
     ap.add_argument("--syrk-dim", type=int, default=SYRK_DIM)
     ap.add_argument("--reps", type=int, default=30)

@@ -14,6 +14,7 @@ struct GemmParams {
   int M, N, K;
   int sym;        // 1: triangular schedule + mirrored store (requires A == B, M == N)
   int tiles_m;    // row tiles of the schedule
+  int tiles_n;    // CTA-pair kernel, general products: > 0 = column tiles, tiles walk along columns first
   int num_tiles;  // length of the static tile list
   int num_kb;     // ceil(K / 64)
   int strip_w;    // CTA-pair kernel, symmetric lists: width of the column strips (0: column order)

@@ -260,6 +260,7 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
   p.sym = a.sym;
   p.tiles_m = (p.M + 127) / 128;
+  p.tiles_n = 0;
   p.num_kb = (p.K + BK - 1) / BK;
   p.num_tiles = 0;
   p.D = a.D; p.ldd = a.ldd;

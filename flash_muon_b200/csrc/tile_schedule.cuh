@@ -3,7 +3,7 @@
 // computed exactly once (tests/schedule_check.cpp does; it includes this file with a plain C++
 // compiler).  The functions are templated on the parameter struct: the kernels pass GemmParams,
 // a host check passes any struct with the same schedule fields
-//   M, N, sym, tiles_m, num_tiles, num_kb, strip_w, sk_dp_tiles, sk_per, sk_total.
+//   M, N, sym, tiles_m, tiles_n, num_tiles, num_kb, strip_w, sk_dp_tiles, sk_per, sk_total.
 #pragma once
 #include <math.h>
 
@@ -105,10 +105,20 @@ template <class P>
 FM_HD Tile2 decode_tile2(const P& p, int t) {
   Tile2 o;
   if (!p.sym) {
-    const int tn = t / p.tiles_m;
-    const int tm = t - tn * p.tiles_m;
-    o.m0 = tm * 256;
-    o.n0 = tn * 256;
+    // Consecutive tiles (which run at the same time) walk along the dimension with FEWER tiles, so
+    // that a wave re-reads the panels of the smaller operand (they stay in L2) and streams the
+    // panels of the larger one once; tiles_n > 0 selects the walk along columns.
+    if (p.tiles_n > 0) {
+      const int tm = t / p.tiles_n;
+      const int tn = t - tm * p.tiles_n;
+      o.m0 = tm * 256;
+      o.n0 = tn * 256;
+    } else {
+      const int tn = t / p.tiles_m;
+      const int tm = t - tn * p.tiles_m;
+      o.m0 = tm * 256;
+      o.n0 = tn * 256;
+    }
   } else if (p.strip_w > 0) {
     const int w = p.strip_w;
     int s = 0;

@@ -129,17 +129,21 @@ class Muon(torch.optim.Optimizer):
         return n
 
     def _plan(self, group, native: bool) -> tuple[int, int]:
-        """(lanes, batch) of a group: the single-call step batches narrow matrices (as many as
-        fill one wave of CTA pairs with the tiles of ``X @ X.T``) over two lanes; the round loop
-        runs one matrix per round, narrow ones over four lanes."""
+        """(lanes, batch) of a group.  The single-call step sends narrow matrices through
+        Newton-Schulz several at a time -- as many as fill two waves of CTA pairs with the tiles
+        of ``X @ X.T``: 14 matrices of 1024 rows, 4 of 2048 -- and matrices that fill the GPU alone
+        (3072 rows or more) one at a time, both over two lanes.  The round loop runs one matrix
+        per round, narrow ones over four lanes."""
         narrow = self._narrow(group)
         if native:
             t = -(-narrow // 256)
-            batch = max(1, min(self._max_batch, self._pairs() // (t * (t + 1) // 2)))
-            forced = os.environ.get("FM_MUON_BATCH")
+            small = 2 * (self._pairs() // (t * (t + 1) // 2))
+            batch = min(self._max_batch, small) if small >= 2 else 1
+            forced = os.environ.get("FM_MUON_BATCH" if small >= 2 else "FM_MUON_BATCH_LARGE")
             if forced:
                 batch = max(1, min(16, int(forced)))
-            return 2, batch
+            lanes = max(1, min(4, int(os.environ.get("FM_MUON_LANES", "2"))))
+            return lanes, batch
         return (4 if narrow <= self._small_dim else self._large_lanes), 1
 
     def _group_buffers(self, gi: int, count: int):

@@ -25,7 +25,7 @@
 namespace {
 
 struct Sched {
-  int M, N, sym, tiles_m, num_tiles, num_kb, strip_w, sk_dp_tiles, sk_per;
+  int M, N, sym, tiles_m, tiles_n, num_tiles, num_kb, strip_w, sk_dp_tiles, sk_per;
   long long sk_total;
 };
 
@@ -74,10 +74,11 @@ void check_single(int M, int N, int sym) {
   ++g_checked;
 }
 
-void check_pair_list(int M, int N, int sym, int strip_w = 0) {
+void check_pair_list(int M, int N, int sym, int strip_w = 0, bool columns_first = false) {
   Sched p{};
   p.M = M; p.N = N; p.sym = sym; p.strip_w = strip_w;
   p.tiles_m = (M + 255) / 256;
+  p.tiles_n = (!sym && columns_first) ? (N + 255) / 256 : 0;  // general products: walk along columns first
   p.num_tiles = fm::count_tiles2(M, N, sym);
   const int bn = (N + 255) / 256;
   std::vector<int> cover((size_t)p.tiles_m * bn, 0);
@@ -193,6 +194,7 @@ int main() {
           check_single<128>(m, n, 0);
           check_single<256>(m, n, 0);
           check_pair_list(m, n, 0);
+          check_pair_list(m, n, 0, 0, true);
         }
       }
     }
