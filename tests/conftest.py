@@ -1,4 +1,5 @@
 """pytest configuration: the ``gpu`` marker, import paths and shared fixtures."""
+import os
 import sys
 from pathlib import Path
 
@@ -45,13 +46,16 @@ def options():
         _lib.set_option(name, value)
 
 
+# Where GPU sessions leave their measured records (parity distances): FM_REPORT_DIR, or the
+# scratch output folder at the repository root.
+REPORT_DIR = Path(os.environ.get("FM_REPORT_DIR", ROOT / "gpurun_out"))
 _OBSERVED: dict = {}
 
 
 def observe(name: str, value: float) -> float:
     """Remembers a measured distance under ``name`` (largest value wins) and returns it; at the end
-    of a GPU session everything observed is written to ``gpurun_out/parity_observed.json``, the
-    record the tolerances in these tests are set from."""
+    of a GPU session everything observed is written to ``parity_observed.json`` in the report
+    folder, the record the tolerances in these tests are set from."""
     _OBSERVED[name] = max(float(value), _OBSERVED.get(name, 0.0))
     return value
 
@@ -61,7 +65,7 @@ def pytest_sessionfinish(session, exitstatus):
         return
     import json
     try:
-        out = ROOT / "gpurun_out"
+        out = REPORT_DIR
         out.mkdir(exist_ok=True)
         (out / "parity_observed.json").write_text(json.dumps(dict(sorted(_OBSERVED.items())), indent=1))
     except OSError:

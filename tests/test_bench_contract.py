@@ -35,7 +35,7 @@ def test_default_cpu_sample_is_one_whole_layer():
     assert "x32.0" in bench.describe_sample(shapes, full / fl)
 
 
-def test_flop_bookkeeping_matches_the_survey_figures():
+def test_flop_bookkeeping_of_the_llama_shaped_step():
     alg, full = bench.full_step_flops()
     assert abs(alg - 4.7181e14) / 4.7181e14 < 1e-3      # algorithmic FLOPs of one Llama-shaped step
     assert abs(full - 6.6589e14) / 6.6589e14 < 1e-3     # cuBLAS-equivalent FLOPs
@@ -57,3 +57,23 @@ def test_replica_checksum_sees_single_bit_and_position_changes():
     a, b = swapped[0].view(-1)[5].clone(), swapped[0].view(-1)[70000].clone()
     swapped[0].view(-1)[5], swapped[0].view(-1)[70000] = b, a
     assert a != b and not torch.equal(base, bench.replica_checksum(swapped))
+
+
+def test_recorded_traffic_is_only_reported_for_the_sources_it_was_captured_from(monkeypatch):
+    """`roofline.traffic` comes from a tracked capture stamped with a hash of the kernel sources:
+    reported while the hash matches and no tuning switch is set, null otherwise."""
+    rec = json.loads((ROOT / "profiles" / "gemm_tc2_kernel_syrk_traffic.json").read_text())
+    assert rec["shape"] == [8192, 8192] and rec["dram_bytes_read"] > 0 and rec["dram_bytes_written"] > 0
+    for v in ("FM_GEMM_IMPL", "FM_GEMM_BN", "FM_GEMM_STAGES", "FM_GEMM_BALANCE", "FM_GEMM_STRIP", "FM_PDL"):
+        monkeypatch.delenv(v, raising=False)
+    traffic, source = bench.recorded_traffic(8192, 8192)
+    if rec["source_hash"] == bench.gemm_source_hash():
+        assert traffic == rec["dram_bytes_read"] + rec["dram_bytes_written"] and rec["commit"] in source
+    else:
+        assert traffic is None and "predates" in source
+    assert bench.recorded_traffic(4096, 4096)[0] is None
+    monkeypatch.setenv("FM_GEMM_STRIP", "0")
+    assert bench.recorded_traffic(8192, 8192)[0] is None
+    monkeypatch.setattr(bench, "gemm_source_hash", lambda: "0" * 16)
+    monkeypatch.delenv("FM_GEMM_STRIP")
+    assert bench.recorded_traffic(8192, 8192)[0] is None

@@ -41,7 +41,7 @@ def test_small_case_against_reference_golden(golden):
         # compare the applied change: parameters move by ~lr per step, so the raw tensors would
         # agree to 1e-2 even with a wrong update
         d_mine, d_ref = p.detach().cpu().float() - p0.float(), r.float() - p0.float()
-        assert observe("muon_golden/update_vs_reference_cpu", rel_fro(d_mine, d_ref)) <= 5e-2
+        assert observe("muon_golden/update_vs_reference_cpu", rel_fro(d_mine, d_ref)) <= 8e-3  # observed 5.3e-3
         assert rel_fro(p, r) <= 1e-2
     for p, r in zip(ps, golden["muon_step/ws1/momentum"]):
         got = opt.state[p]["momentum_buffer"].cpu()
@@ -63,7 +63,7 @@ def test_against_torch_restatement_on_cuda(nesterov, dt):
     ps, opt = run_product(params, grads, steps, **hp)
     for i, (p, r, p0) in enumerate(zip(ps, ref, params)):
         d_mine, d_ref = p.detach().float() - p0.to(DEV).float(), r.float() - p0.to(DEV).float()
-        assert observe("muon_small/update_vs_torch_cuda", rel_fro(d_mine, d_ref)) <= 5e-2
+        assert observe("muon_small/update_vs_torch_cuda", rel_fro(d_mine, d_ref)) <= 2e-3  # observed 0
         # elementwise state is bit-exact: momentum buffers and the gradient overwritten in place
         assert torch.equal(opt.state[p]["momentum_buffer"], bufs[i])
         assert torch.equal(p.grad, ref_grads[i])
@@ -88,9 +88,10 @@ def test_config3_gpt2_medium_shapes_one_step():
     for p, r, l, p0 in zip(ps, ref, loose, params):
         base = p0.to(DEV).float()
         d_mine, d_ref, d_loose = p.detach().float() - base, r.float() - base, l.float() - base
-        assert observe("muon_gpt2/update_vs_torch_cuda", rel_fro(d_mine, d_ref)) <= 2e-2
+        assert observe("muon_gpt2/update_vs_torch_cuda", rel_fro(d_mine, d_ref)) <= 2e-3  # observed 0
         # another accumulation order of the same fp32 sums moves a 5-step bf16 iterate of a
-        # 1024-wide matrix by a few percent: that is the floor, the kernels are not further away
+        # 1024-wide matrix by a few percent (observed 4.2e-2 for both, which are the same number
+        # because the product equals the torch formulation bit for bit): that is the floor
         assert observe("muon_gpt2/update_vs_exact_fp32_sums", rel_fro(d_mine, d_loose)) <= 6e-2
         assert observe("muon_gpt2/torch_cuda_vs_exact_fp32_sums", rel_fro(d_ref, d_loose)) <= 6e-2
     _lib.device_status()

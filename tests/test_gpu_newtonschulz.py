@@ -41,8 +41,9 @@ def test_golden_cases(golden, shape, steps):
     assert out.dtype == torch.bfloat16 and out.shape == G.shape
     ref = golden[f"fast_newtonschulz/{shape[0]}x{shape[1]}/steps{steps}"]
     # tiny matrices sit on a higher bf16 noise floor than the 4096^2 config the 2e-2 bar is set
-    # on: the reference's own two formulations differ by 3.5e-2 here (see test_oracle_golden)
-    tol = TOL_STEPS[steps] if steps < 5 else 4e-2
+    # on (the reference's own two formulations differ by 3.5e-2 here, see test_oracle_golden);
+    # observed on B200: 0 for three of the four shapes, 1.44e-2 for 128 x 128 -> 1.5 x that
+    tol = TOL_STEPS[steps] if steps < 5 else 2.2e-2
     assert observe(f"ns_golden/{shape[0]}x{shape[1]}/steps{steps}/vs_reference_cpu", rel_fro(out, ref)) <= tol
     assert observe(f"ns_golden/steps{steps}/vs_torch_cuda", rel_fro(out, torch_cuda_ns(G.to(DEV), steps))) <= 2e-3
     _lib.device_status()
@@ -75,9 +76,11 @@ def test_shapes_and_dtypes_against_torch_cuda(shape, dt):
         out = fm.fast_newtonschulz(G, steps)
         ref = torch_cuda_ns(G, steps)
         assert not torch.isnan(out).any()
-        # cuBLAS picks other kernels (another order of the fp32 sums) for sizes off its tile
-        # grid; on small matrices that alone moves a 5-step bf16 iterate by 2-3e-2
-        tol = 2e-2 if min(shape) >= 1024 else 4e-2
+        # 1024-wide shapes: bit-identical to the torch formulation (observed 0).  cuBLAS picks
+        # other kernels (another order of the fp32 sums) for sizes off its tile grid; on small
+        # matrices that alone moves a 5-step bf16 iterate by up to 2.5e-2 (observed), 2.2e-4
+        # after one step; bounds are 1.5 x the observed values
+        tol = 2e-3 if min(shape) >= 1024 else {0: 1e-3, 1: 1e-3, 5: 3.7e-2}[steps]
         cls = "wide1024" if min(shape) >= 1024 else "small"
         assert observe(f"ns_shapes/{cls}/steps{steps}/vs_torch_cuda", rel_fro(out, ref)) <= tol, (shape, dt, steps)
     _lib.device_status()
@@ -87,8 +90,8 @@ def test_shapes_and_dtypes_against_torch_cuda(shape, dt):
 def test_against_cpu_oracle(shape):
     G = torch.randn(*shape, generator=torch.Generator().manual_seed(shape[0] + 3 * shape[1]))
     out = fm.fast_newtonschulz(G.to(DEV), 5)
-    # 1024-wide shapes: noise floor ~1.8e-2
-    assert observe(f"ns_cpu_oracle/{shape[0]}x{shape[1]}/steps5", rel_fro(out, O.newtonschulz(G, 5))) <= 2.5e-2
+    # two orders of the same fp32 sums: observed 9.2e-3 ... 1.26e-2 on B200 -> 1.5 x the largest
+    assert observe(f"ns_cpu_oracle/{shape[0]}x{shape[1]}/steps5", rel_fro(out, O.newtonschulz(G, 5))) <= 1.9e-2
 
 
 @pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (4096, 14336), (14336, 4096)])
@@ -104,7 +107,7 @@ def test_full_size_properties(shape):
     # a square Gaussian matrix has singular values down to ~0, which five steps cannot lift;
     # the bulk must still have been pushed into the band
     assert (sv > 0.5).double().mean() > (0.97 if shape[0] != shape[1] else 0.85), sv.min().item()
-    assert observe("ns_full_size/steps5/vs_torch_cuda", rel_fro(out, torch_cuda_ns(G, 5))) <= 2e-2
+    assert observe("ns_full_size/steps5/vs_torch_cuda", rel_fro(out, torch_cuda_ns(G, 5))) <= 2e-3  # observed 0
     assert torch.equal(out, fm.fast_newtonschulz(G, 5)), "run-to-run determinism"
     _lib.device_status()
 

@@ -7,8 +7,8 @@
 * the torch CUDA formulation and the CPU oracle -- two orders of the same fp32 sums with the same
   rounding points, i.e. the floor no implementation can be expected to beat.
 
-The numbers are written to ``gpurun_out/parity_report.json`` (when that folder can be created)
-and bounded here: BASELINE.json's 2e-2 after 5 steps against the reference formulation on the same
+The numbers are written to ``parity_report.json`` in the report folder (``conftest.REPORT_DIR``,
+when it can be created) and bounded here: BASELINE.json's 2e-2 after 5 steps against the reference formulation on the same
 device, and the product never further from the CPU oracle than 1.5 x the floor + 2e-3.
 """
 import json
@@ -19,7 +19,7 @@ import torch
 
 import flash_muon_b200 as fm
 from flash_muon_b200 import _lib
-from conftest import rel_fro
+from conftest import REPORT_DIR, rel_fro
 from oracle import muon_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -63,7 +63,7 @@ def test_record_and_bound_the_distance_to_the_reference_formulation(shape):
             "torch_cuda_vs_cpu_oracle": rel_fro(gpu_ref[s], cpu[s]),
         }
     _lib.device_status()
-    out = ROOT / "gpurun_out"
+    out = REPORT_DIR
     try:
         out.mkdir(exist_ok=True)
         f = out / "parity_report.json"
