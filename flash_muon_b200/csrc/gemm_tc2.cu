@@ -78,7 +78,10 @@ __device__ __forceinline__ TileRef locate(const GemmParams& p, int t) {
   return r;
 }
 
-template <typename T>
+// kSplitK: the instantiation that can deposit and gather partial accumulators (balanced tail).
+// Launches that deal whole tiles use the other one, whose epilogue spends the registers of the
+// partial sums on fetching the addend two 32-column chunks ahead instead of one.
+template <typename T, bool kSplitK>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmT,
@@ -276,13 +279,18 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int bi = (tl.m0 >> 7) + (int)rank;
       // tile stores for everything but the diagonal tiles of a symmetric product
       const bool tma_tile = p.tma_store && !(p.sym && tl.m0 == tl.n0);
-      alignas(16) T dcur[32], dnext[32];
-      if (!w.deposit) epilogue_load_d<T>(p, ep, row, tl.n0, dcur);
+      const bool deposit = kSplitK && w.deposit;
+      const bool gather = kSplitK && w.gather;
+      alignas(16) T dcur[32], dnext[32], dnext2[32];
+      if (!deposit) {
+        epilogue_load_d<T>(p, ep, row, tl.n0, dcur);
+        if (!kSplitK) epilogue_load_d<T>(p, ep, row, tl.n0 + 32, dnext);
+      }
 
       // parts of this tile deposited by earlier pairs: pairs c_first .. pair-1
       int c_first = pair;
       unsigned int* cnt = nullptr;
-      if (w.gather) {
+      if (gather) {
         c_first = (int)(((long long)w.sk_tile * p.num_kb) / p.sk_per);
         cnt = p.sk_cnt + (w.sk_tile * 2 + (int)rank);
         if (threadIdx.x == 64) {
@@ -324,24 +332,28 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
         }
       };
-      if (w.gather) load_parts(0, psum);
+      if (gather) load_parts(0, psum);
 
       bool ok = ptx::mbar_wait(tfull_bar(acc), acc_ph, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after();
       const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 256);
-      if (!w.deposit) {
+      if (!deposit) {
 #pragma unroll 1
         for (int ch = 0; ch < 8; ++ch) {
           uint32_t raw[32];
           ptx::tmem_ld_32x32(t_acc + (uint32_t)(ch * 32), raw);
-          if (ch + 1 < 8) {
-            epilogue_load_d<T>(p, ep, row, tl.n0 + (ch + 1) * 32, dnext);
-            if (w.gather) load_parts(ch + 1, pnext);
+          if (kSplitK) {
+            if (ch + 1 < 8) {
+              epilogue_load_d<T>(p, ep, row, tl.n0 + (ch + 1) * 32, dnext);
+              if (gather) load_parts(ch + 1, pnext);
+            }
+          } else if (ch + 2 < 8) {
+            epilogue_load_d<T>(p, ep, row, tl.n0 + (ch + 2) * 32, dnext2);
           }
           ptx::tmem_ld_wait();
-          if (w.gather) {
+          if (gather) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(psum[j] + __uint_as_float(raw[j]));
           }
@@ -376,8 +388,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
             for (int v = 0; v < 4; ++v)
               reinterpret_cast<uint4*>(dcur)[v] = reinterpret_cast<const uint4*>(dnext)[v];
+            if (!kSplitK) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                reinterpret_cast<uint4*>(dnext)[v] = reinterpret_cast<const uint4*>(dnext2)[v];
+            }
           }
-          if (w.gather) {
+          if (gather) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) psum[j] = pnext[j];
           }
@@ -403,7 +420,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
 
-      if (w.deposit) {
+      if (deposit) {
         // publish the deposit: all 128 threads' stores first, then one count
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -459,7 +476,9 @@ int max_pairs_for() {
     constexpr int kMost = smem_bytes(kMaxStages, false) > smem_bytes(kMaxStagesWithStaging, true)
                               ? smem_bytes(kMaxStages, false)
                               : smem_bytes(kMaxStagesWithStaging, true);
-    if (cudaFuncSetAttribute(gemm_tc2_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tc2_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kMost) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_tc2_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kMost) != cudaSuccess)
       return 0;
     cudaLaunchConfig_t cfg = {};
@@ -474,7 +493,7 @@ int max_pairs_for() {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<T>, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<T, true>, &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = sm_count() / 2;
     }
@@ -544,7 +563,10 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& t
     cfg.numAttrs = 2;
   }
   cfg.attrs = attr;
-  FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T>, tmA, tmB, tmC, tmT, p));
+  if (p.sk_per > 0)
+    FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T, true>, tmA, tmB, tmC, tmT, p));
+  else
+    FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T, false>, tmA, tmB, tmC, tmT, p));
   return FM_OK;
 }
 

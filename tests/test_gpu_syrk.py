@@ -209,6 +209,39 @@ def test_dependent_launches_see_their_predecessor(pdl, options):
     _lib.device_status()
 
 
+@pytest.mark.parametrize("name,value", [("gemm_kb_per_stage", 1), ("gemm_kb_per_stage", 3), ("gemm_stages", 4),
+                                        ("gemm_stages", 7), ("gemm_tma_store", 0), ("pdl_trigger", 1),
+                                        ("pdl_trigger", 2), ("pdl", 0), ("gemm_l2_promotion", 0)])
+def test_pipeline_and_store_switches_change_no_bit(name, value, options):
+    """Ring depth, K blocks per stage, TMA or per-lane stores, dependent-launch trigger: all of
+    them change how a tile is fed and written, none the order of any sum.  Symmetric product with
+    ragged edges and a general product with addend and both outputs, against the defaults."""
+    lib = _lib.lib
+    g = torch.Generator(device=DEV).manual_seed(31)
+    x = (torch.randn(2500, 1100 + 8, device=DEV, generator=g) / 33).bfloat16()[:, :1096]   # pitch 1104
+    M, N, K = 1000, 1800, 520
+    A = (torch.randn(M, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    B = torch.randn(N, K, device=DEV, generator=g).bfloat16()
+    D = torch.randn(M, N, device=DEV, generator=g).bfloat16()
+
+    def run():
+        y = fm.matmul_transpose(x)
+        C = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        CT = torch.full((N, M), float("nan"), device=DEV, dtype=torch.bfloat16)
+        _lib.check(lib.fm_gemm_nt(A.data_ptr(), K, B.data_ptr(), K, M, N, K, D.data_ptr(), N, 3.4445, 1.0,
+                                  C.data_ptr(), N, CT.data_ptr(), M, 0, 0, 0))
+        return y, C, CT
+
+    options("gemm_impl", 2)
+    ref = run()
+    options(name, value)
+    got = run()
+    for a, b in zip(ref, got):
+        assert not torch.isnan(a).any() and torch.equal(a, b)
+    assert torch.equal(got[2], got[1].T)
+    _lib.device_status()
+
+
 def test_empty_and_degenerate():
     assert fm.matmul_transpose(torch.empty(0, 16, device=DEV, dtype=torch.bfloat16)).shape == (0, 0)
     y = fm.matmul_transpose(torch.empty(5, 0, device=DEV, dtype=torch.bfloat16))
