@@ -281,10 +281,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const bool tma_tile = p.tma_store && !(p.sym && tl.m0 == tl.n0);
       const bool deposit = kSplitK && w.deposit;
       const bool gather = kSplitK && w.gather;
-      alignas(16) T dcur[32], dnext[32], dnext2[32];
+      // Addend values of the chunks to come: dq[0] is the chunk being processed, dq[kAhead] the
+      // one whose loads go out now.
+      constexpr int kAhead = kSplitK ? 1 : 2;  // measured: 3 and 4 are slower again at K = 1024
+      alignas(16) T dq[kAhead + 1][32];
       if (!deposit) {
-        epilogue_load_d<T>(p, ep, row, tl.n0, dcur);
-        if (!kSplitK) epilogue_load_d<T>(p, ep, row, tl.n0 + 32, dnext);
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) epilogue_load_d<T>(p, ep, row, tl.n0 + a * 32, dq[a]);
       }
 
       // parts of this tile deposited by earlier pairs: pairs c_first .. pair-1
@@ -344,14 +347,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int ch = 0; ch < 8; ++ch) {
           uint32_t raw[32];
           ptx::tmem_ld_32x32(t_acc + (uint32_t)(ch * 32), raw);
-          if (kSplitK) {
-            if (ch + 1 < 8) {
-              epilogue_load_d<T>(p, ep, row, tl.n0 + (ch + 1) * 32, dnext);
-              if (gather) load_parts(ch + 1, pnext);
-            }
-          } else if (ch + 2 < 8) {
-            epilogue_load_d<T>(p, ep, row, tl.n0 + (ch + 2) * 32, dnext2);
-          }
+          if (ch + kAhead < 8) epilogue_load_d<T>(p, ep, row, tl.n0 + (ch + kAhead) * 32, dq[kAhead]);
+          if (gather && ch + 1 < 8) load_parts(ch + 1, pnext);
           ptx::tmem_ld_wait();
           if (gather) {
 #pragma unroll
@@ -359,12 +356,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           const int c0 = tl.n0 + ch * 32;
           if (!tma_tile) {
-            epilogue_store<T>(p, ep, raw, dcur, row, c0, bi);
+            epilogue_store<T>(p, ep, raw, dq[0], row, c0, bi);
           } else if (row0w < p.M && (c0 & ~63) < p.N) {  // warp-uniform: something of this 64-column pair is inside
             const int half = ch & 1;
             if (c0 < p.N) {
               alignas(16) T outv[32];
-              epilogue_values<T>(p, ep, raw, dcur, outv);
+              epilogue_values<T>(p, ep, raw, dq[0], outv);
               if (half == 0) {  // the previous stores of this warp have let go of the staging tiles
                 if (lane == 0) ptx::bulk_wait_read_all();
                 __syncwarp();
@@ -386,12 +383,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           if (ep.D != nullptr) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v)
-              reinterpret_cast<uint4*>(dcur)[v] = reinterpret_cast<const uint4*>(dnext)[v];
-            if (!kSplitK) {
+            for (int a = 0; a < kAhead; ++a) {
 #pragma unroll
               for (int v = 0; v < 4; ++v)
-                reinterpret_cast<uint4*>(dnext)[v] = reinterpret_cast<const uint4*>(dnext2)[v];
+                reinterpret_cast<uint4*>(dq[a])[v] = reinterpret_cast<const uint4*>(dq[a + 1])[v];
             }
           }
           if (gather) {

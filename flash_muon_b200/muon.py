@@ -132,13 +132,14 @@ class Muon(torch.optim.Optimizer):
         """(lanes, batch) of a group.  The single-call step sends narrow matrices through
         Newton-Schulz several at a time -- as many as fill two waves of CTA pairs with the tiles
         of ``X @ X.T``: 14 matrices of 1024 rows, 4 of 2048 -- and matrices that fill the GPU alone
-        (3072 rows or more) one at a time, both over two lanes.  The round loop runs one matrix
-        per round, narrow ones over four lanes."""
+        (3072 rows or more) two at a time (tile lists twice as long leave a smaller share of a
+        wave idle at their end, and half as many kernel boundaries), both over two lanes.  The
+        round loop runs one matrix per round, narrow ones over four lanes."""
         narrow = self._narrow(group)
         if native:
             t = -(-narrow // 256)
             small = 2 * (self._pairs() // (t * (t + 1) // 2))
-            batch = min(self._max_batch, small) if small >= 2 else 1
+            batch = min(self._max_batch, small) if small >= 2 else 2
             forced = os.environ.get("FM_MUON_BATCH" if small >= 2 else "FM_MUON_BATCH_LARGE")
             if forced:
                 batch = max(1, min(16, int(forced)))
