@@ -541,9 +541,11 @@ def run_ours(args):
             passes = -(-len(grp["params"]) // batch)
             launches_per_step += passes * (1 + 1 + 3 * HP["ns_steps"] + 1)
     else:
-        # round loop: per owned matrix 1 momentum, 1 normalisation, 3 GEMMs per iteration; one
-        # decay + update per owned matrix (owners push parameters) or per round
-        launches_per_step = len(owned) * (1 + 1 + 3 * HP["ns_steps"]) + (len(owned) if pushes_params else rounds)
+        # round loop: 1 momentum per owned matrix; per Newton-Schulz pass (the matrices a rank owns
+        # in up to eight consecutive rounds) 1 normalisation and 3 GEMMs per iteration; one decay +
+        # update per owned matrix (owners push parameters) or per round
+        passes = sum(-(-(-(-len(grp["params"]) // ws)) // opt._loop_plan(grp)[1]) for grp in opt.param_groups)
+        launches_per_step = len(owned) + passes * (1 + 3 * HP["ns_steps"]) + (len(owned) if pushes_params else rounds)
     alg, full = full_step_flops()
     alg, full = alg * args.layers / N_LAYERS, full * args.layers / N_LAYERS
 

@@ -53,6 +53,7 @@ from .ops import fast_newtonschulz, newtonschulz_workspace_bytes
 __all__ = ["Muon"]
 
 _NATIVE_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
+_lib_flags_sumsq_ready = 2  # FM_NS_FAITHFUL | FM_NS_SUMSQ_READY
 
 
 class Muon(torch.optim.Optimizer):
@@ -82,6 +83,7 @@ class Muon(torch.optim.Optimizer):
     _small_dim = 1536          # round loop: groups at most this narrow get 4 lanes
     _large_lanes = 2           # lanes of the other groups
     _max_batch = 16            # matrices per batched Newton-Schulz pass (single-call step)
+    _rounds_per_pass = 0       # round loop: > 0 fixes the rounds per pass (tests), 0 = by plan
     # Host-side deadline of the copy-engine exchange: a peer that has not taken part in a step
     # this long after the step was enqueued is taken for gone (NCCL's watchdog default is of
     # the same order).  FM_MUON_PEER_TIMEOUT=<seconds> overrides it, 0 switches it off.
@@ -147,6 +149,24 @@ class Muon(torch.optim.Optimizer):
             return lanes, batch
         return (4 if narrow <= self._small_dim else self._large_lanes), 1
 
+    def _loop_plan(self, group) -> tuple[int, int, int]:
+        """(lanes, rounds per pass, gather buffers) of a group in the round loop.  The matrices a
+        rank owns in consecutive rounds go through Newton-Schulz together like in the single-call
+        step (at most eight rounds per pass); every round of a pass writes its own gather buffer,
+        and two passes' worth of buffers let the next pass start while the rounds of the previous
+        one are still being exchanged and applied."""
+        lanes = self._plan(group, False)[0]
+        rounds = -(-len(group["params"]) // self.world_size)
+        per_pass = 1
+        if self._rounds_per_pass > 0:
+            per_pass = min(self._rounds_per_pass, rounds)
+        elif self._overlap_updates and self._two_lanes and self._stock_device_ops() \
+                and group["update_buffer"].is_cuda and os.environ.get("FM_MUON_LOOP_BATCH", "1") != "0":
+            per_pass = max(1, min(8, self._plan(group, True)[1], rounds))
+        if per_pass > 1:
+            lanes = 2
+        return lanes, per_pass, max(2 * lanes, 2 * per_pass)
+
     def _group_buffers(self, gi: int, count: int):
         """``count`` gather buffers of group ``gi`` in rotation order and their per-rank views: the
         group's own ``update_buffer`` first, the rest from a pool outside ``param_groups``."""
@@ -186,6 +206,50 @@ class Muon(torch.optim.Optimizer):
         rows, cols = g.shape
         fast_newtonschulz(g, steps=steps, out=out.view(rows, cols),
                           workspace=self._ns_workspace(rows, cols, g.device), sumsq_ready=sumsq_ready)
+
+    def _momentum_and_orthogonalize(self, items, group, fused: bool) -> None:
+        """Momentum + Newton-Schulz of the matrices this rank owns in the rounds of one pass:
+        ``items`` holds (gradient, momentum buffer, slot) per matrix.  Matrices that share their
+        smaller and larger dimension go through ``fm_newtonschulz_batched`` together; anything
+        else (one matrix, overridden device operations, mixed shapes) one at a time."""
+        mom, nes, steps = group["momentum"], group["nesterov"], group["ns_steps"]
+        dims = {(min(g.size(0), g.numel() // max(g.size(0), 1)), max(g.size(0), g.numel() // max(g.size(0), 1)),
+                 g.dtype) for g, _, _ in items}
+        native = fused and all(g.ndim in (2, 4) and g.numel() > 0 and g.dtype in _NATIVE_DTYPES
+                               and g.is_contiguous() for g, _, _ in items)
+        if not (native and len(items) > 1 and len(dims) == 1):
+            for g, buf, slot in items:
+                rows = g.size(0)
+                cols = g.numel() // max(rows, 1)
+                if native:
+                    wsp = self._ns_workspace(rows, cols, g.device)
+                    part = wsp.data_ptr() + int(lib.fm_ns_partials_offset(rows, cols))
+                    g = self._momentum(g, buf, mom, nes, part)
+                else:
+                    g = self._momentum(g, buf, mom, nes)
+                if g.ndim == 4:  # for the case of conv filters
+                    g = g.view(len(g), -1)
+                if native:
+                    self._orthogonalize(g, slot, steps, True)
+                else:
+                    self._orthogonalize(g, slot, steps)
+            return
+        n = len(items)
+        g0 = items[0][0]
+        rows = [g.size(0) for g, _, _ in items]
+        cols = [g.numel() // r for (g, _, _), r in zip(items, rows)]
+        need = int(lib.fm_ns_batched_workspace_bytes(n, rows[0], cols[0]))
+        wsp = self._workspaces.get(self._lane)
+        if wsp is None or wsp.numel() < need or wsp.device != g0.device:
+            self._workspaces[self._lane] = wsp = torch.empty(need, dtype=torch.uint8, device=g0.device)
+        part = wsp.data_ptr() + int(lib.fm_ns_batched_partials_offset(n, rows[0], cols[0]))
+        stride = 4 * int(lib.fm_norm_scratch_floats())
+        srcs = [self._momentum(g, buf, mom, nes, part + j * stride) for j, (g, buf, _) in enumerate(items)]
+        check(lib.fm_newtonschulz_batched(
+            (ctypes.c_void_p * n)(*[t.data_ptr() for t in srcs]), (ctypes.c_int64 * n)(*rows),
+            (ctypes.c_int64 * n)(*cols), n, dtype_code(g0.dtype), int(steps),
+            (ctypes.c_void_p * n)(*[slot.data_ptr() for _, _, slot in items]), wsp.data_ptr(),
+            wsp.numel(), _lib_flags_sumsq_ready, current_stream_ptr(g0.device)))
 
     def _all_gather(self, buffer: Tensor, slot: Tensor):
         # in place: `slot` is row `rank` of `buffer`                    (flash_muon/muon.py:108)
@@ -248,7 +312,7 @@ class Muon(torch.optim.Optimizer):
         return bool(torch.equal(lo, hi))
 
     def _peer_pointers(self):
-        bufs = [[b.data_ptr() for b in self._group_buffers(gi, 2 * self._plan(g, False)[0])[0]]
+        bufs = [[b.data_ptr() for b in self._group_buffers(gi, self._loop_plan(g)[2])[0]]
                 for gi, g in enumerate(self.param_groups)]
         pars = [[p.data_ptr() for p in g["params"]] for g in self.param_groups]
         return bufs, pars
@@ -454,8 +518,8 @@ class Muon(torch.optim.Optimizer):
         if peer is not None:
             peer.begin_step(torch.cuda.current_stream(self.param_groups[0]["update_buffer"].device))
         for gi, group in enumerate(self.param_groups):
-            nlanes = self._plan(group, False)[0]
-            buffers, views = self._group_buffers(gi, 2 * nlanes)
+            nlanes, per_pass, nbuf_want = self._loop_plan(group)
+            buffers, views = self._group_buffers(gi, nbuf_want)
             nbuf = len(buffers)
             params: list[Tensor] = group["params"]
             handle = None
@@ -509,60 +573,58 @@ class Muon(torch.optim.Optimizer):
                     upd_done[prev] = torch.cuda.Event()
                     upd_done[prev].record(side)
 
-            for round_idx, base_i in enumerate(range(0, len(params), ws)):
-                cur = round_idx % nbuf
-                slot = views[cur][self.rank]
-                # buffer `cur` always travels on lane `cur % nlanes`
-                lane = lanes[cur % nlanes] if lanes is not None else (main if overlap else None)
-                self._lane = (cur % nlanes) if lanes is not None else 0
+            bases = list(range(0, len(params), ws))
+            for pass_idx, r0 in enumerate(range(0, len(bases), per_pass)):
+                rounds = bases[r0: r0 + per_pass]
+                # a pass travels on one lane; its rounds use consecutive gather buffers
+                lane = lanes[pass_idx % nlanes] if lanes is not None else (main if overlap else None)
+                self._lane = (pass_idx % nlanes) if lanes is not None else 0
                 with (torch.cuda.stream(lane) if lanes is not None else contextlib.nullcontext()):
-                    if overlap and upd_done[cur] is not None:
-                        lane.wait_event(upd_done[cur])  # buffer `cur` is free to be overwritten
-                        upd_done[cur] = None
-                    if peer is not None:
-                        peer.before_slot_write(gi, cur, torch.cuda.current_stream(slot.device))
-                    if base_i + self.rank < len(params):
-                        p = params[base_i + self.rank]
-                        g = p.grad
-                        assert g is not None
-                        if grad_ready is not None and p in grad_ready:
-                            torch.cuda.current_stream(g.device).wait_event(grad_ready[p])
-                        state = self.state[p]
-                        if "momentum_buffer" not in state:
-                            state["momentum_buffer"] = torch.zeros_like(g)
-                        buf: Tensor = state["momentum_buffer"]
-                        rows = g.size(0)
-                        cols = g.numel() // max(rows, 1)
-                        if fused and g.ndim in (2, 4) and g.numel() > 0 and g.dtype in _NATIVE_DTYPES:
-                            wsp = self._ns_workspace(rows, cols, g.device)
-                            part = wsp.data_ptr() + int(lib.fm_ns_partials_offset(rows, cols))
-                            g = self._momentum(g, buf, group["momentum"], group["nesterov"], part)
-                            if g.ndim == 4:  # for the case of conv filters
-                                g = g.view(len(g), -1)
-                            self._orthogonalize(g, slot, group["ns_steps"], True)
-                        else:
-                            g = self._momentum(g, buf, group["momentum"], group["nesterov"])
-                            if g.ndim == 4:  # for the case of conv filters
-                                g = g.view(len(g), -1)
-                            self._orthogonalize(g, slot, group["ns_steps"])
-                        if overlap:
-                            ns_done[cur] = torch.cuda.Event()
-                            ns_done[cur].record(lane)
-                    else:
+                    # -- this rank's matrices of the pass: momentum + Newton-Schulz into their slots
+                    items, curs = [], []
+                    for k, base_i in enumerate(rounds):
+                        cur = (r0 + k) % nbuf
+                        if overlap and upd_done[cur] is not None:
+                            lane.wait_event(upd_done[cur])  # buffer `cur` is free to be overwritten
+                            upd_done[cur] = None
+                        if peer is not None:
+                            peer.before_slot_write(gi, cur, torch.cuda.current_stream(views[cur][self.rank].device))
                         ns_done[cur] = None
-                    # an idle rank contributes whatever its slot holds (muon.py:104-105)
-                    if base_i > 0:
-                        update_prev()
-                    if push_params:
-                        handle = None  # published by update_prev, after the owner's update
-                    elif peer is not None:
-                        handle = peer.publish(gi, cur, slot.data_ptr(), slot.numel() * slot.element_size(),
-                                              list(range(min(ws, len(params) - base_i))))
-                    elif ws > 1:
-                        handle = self._all_gather(buffers[cur], slot)
-                params_world = params[base_i: base_i + ws]
-                prev = cur
-                prev_base = base_i
+                        if base_i + self.rank < len(params):
+                            p = params[base_i + self.rank]
+                            g = p.grad
+                            assert g is not None
+                            if grad_ready is not None and p in grad_ready:
+                                torch.cuda.current_stream(g.device).wait_event(grad_ready[p])
+                            state = self.state[p]
+                            if "momentum_buffer" not in state:
+                                state["momentum_buffer"] = torch.zeros_like(g)
+                            items.append((g, state["momentum_buffer"], views[cur][self.rank]))
+                            curs.append(cur)
+                        # an idle rank contributes whatever its slot holds (muon.py:104-105)
+                    if items:
+                        self._momentum_and_orthogonalize(items, group, fused)
+                        if overlap:
+                            done = torch.cuda.Event()
+                            done.record(lane)
+                            for cur in curs:
+                                ns_done[cur] = done
+                    # -- the rounds of the pass, one exchange each, in the reference's order
+                    for k, base_i in enumerate(rounds):
+                        cur = (r0 + k) % nbuf
+                        slot = views[cur][self.rank]
+                        if params_world is not None:
+                            update_prev()
+                        if push_params:
+                            handle = None  # published by update_prev, after the owner's update
+                        elif peer is not None:
+                            handle = peer.publish(gi, cur, slot.data_ptr(), slot.numel() * slot.element_size(),
+                                                  list(range(min(ws, len(params) - base_i))))
+                        elif ws > 1:
+                            handle = self._all_gather(buffers[cur], slot)
+                        params_world = params[base_i: base_i + ws]
+                        prev = cur
+                        prev_base = base_i
             if params_world is not None:
                 update_prev()
         if overlap:

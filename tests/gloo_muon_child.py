@@ -18,6 +18,7 @@ import flash_muon_b200 as fm  # noqa: E402
 
 class CpuMuon(fm.Muon):
     _buffer_device = "cpu"
+    _rounds_per_pass = int(os.environ.get("TEST_ROUNDS_PER_PASS", "0"))
 
     def _momentum(self, g, buf, momentum, nesterov):
         return O.momentum_update(g, buf, momentum, nesterov)

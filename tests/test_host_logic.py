@@ -62,16 +62,19 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("ws", [1, 2, 3])
-def test_muon_step_control_flow_over_gloo(ws, tmp_path, golden):
+@pytest.mark.parametrize("ws,per_pass", [(1, 0), (2, 0), (3, 0), (1, 3), (2, 2), (3, 4)])
+def test_muon_step_control_flow_over_gloo(ws, per_pass, tmp_path, golden):
     """The product's ``Muon.step`` loop (ownership, double-buffered gather, update order) with its
     device hooks replaced by the oracle, run as ``ws`` CPU ranks: all ranks must end with the
-    reference's parameters, bit for bit, and momentum state must live on the owner only."""
+    reference's parameters, bit for bit, and momentum state must live on the owner only.
+    ``per_pass`` > 0 makes a rank compute the matrices it owns in that many consecutive rounds
+    before the first of those rounds is exchanged (what the loop does on the GPU when it sends
+    them through Newton-Schulz together)."""
     port = _free_port()
     procs = []
     for r in range(ws):
         env = {**os.environ, "RANK": str(r), "WORLD_SIZE": str(ws), "MASTER_ADDR": "127.0.0.1",
-               "MASTER_PORT": str(port), "OMP_NUM_THREADS": "2"}
+               "MASTER_PORT": str(port), "OMP_NUM_THREADS": "2", "TEST_ROUNDS_PER_PASS": str(per_pass)}
         procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "gloo_muon_child.py"),
                                        str(tmp_path / "out")], env=env))
     for p in procs:
