@@ -333,13 +333,13 @@ def time_config1(peaks):
             "frac_of_sustained_peak": alg / t / 1e9 / peaks["bf16_sustained"]}
 
 
-def time_hbm_kernels(peaks):
+def time_hbm_kernels(peaks, log2_n=28):
     """The HBM-bound kernels alone on 2^28 bf16 elements (512 MB per tensor, far beyond L2),
     algorithmic bytes per element over the CUDA-event time, against the measured copy bandwidth."""
     import ctypes
     from flash_muon_b200._lib import lib, check
-    n = 1 << 28
-    rows, cols = 16384, 16384
+    n = 1 << log2_n
+    rows = cols = 1 << (log2_n // 2)
     g = (torch.randn(n, device="cuda") * 1e-3).bfloat16()
     b = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
     p = (torch.randn(n, device="cuda") * 0.02).bfloat16()
@@ -401,6 +401,10 @@ def run_ours(args):
     if args.syrk_only:  # profiling aid: only the matmul_transpose leg
         mt, roof = time_syrk(peaks, args.syrk_dim, args.reps)
         print(json.dumps({"matmul_transpose": mt, "roofline": roof}), flush=True)
+        return
+
+    if args.hbm_only:  # profiling aid: only the HBM-bound kernels
+        print(json.dumps({"hbm_kernels": time_hbm_kernels(peaks, args.hbm_log2)}), flush=True)
         return
 
     shapes = (GPT2_LAYER if args.workload == "gpt2" else LLAMA_LAYER) * args.layers
@@ -631,6 +635,8 @@ def main():
     ap.add_argument("--workload", default="llama", choices=["llama", "gpt2"],
                     help="with --skip-extras: matrix set of the profiled step (gpt2 = configs[3], use --layers 24)")
     ap.add_argument("--syrk-only", action="store_true", help="only the matmul_transpose leg")
+    ap.add_argument("--hbm-only", action="store_true", help="only the HBM-bound kernels")
+    ap.add_argument("--hbm-log2", type=int, default=28, help="log2 of the elements of the HBM-bound leg (even)")
     ap.add_argument("--syrk-dim", type=int, default=SYRK_DIM)
     ap.add_argument("--reps", type=int, default=30)
     args = ap.parse_args()

@@ -31,6 +31,10 @@ template <typename T>
 __device__ __forceinline__ float as_bf16_value(T v) {
   return __bfloat162float(__float2bfloat16_rn(ld_f<T>(v)));
 }
+template <>
+__device__ __forceinline__ float as_bf16_value<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
 
 __device__ __forceinline__ float block_sum_256(float v, float* red /* 8 floats */) {
 #pragma unroll
@@ -167,69 +171,128 @@ scale_transpose_kernel(const __grid_constant__ NormTable tab, int nparts) {
 
 
 // Fast path of the kernel above for matrices whose rows and columns are multiples of 64 and whose
-// pointers and pitches allow 16-byte accesses: every global access is a full 16-byte vector, both
-// outputs are written as whole 128-byte row segments.
+// pointers and pitches allow 16-byte accesses.  A block walks tiles of 128 rows x 64 columns
+// (blockIdx.x, + gridDim.x, ...): it folds the partial sums once, keeps the loads of its next tile
+// in flight while it writes the current one, writes X in 128-byte and the transposed copy in
+// 256-byte row segments, every access a full 16-byte vector.
+constexpr int kScaleTileRows = 128;
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, sizeof(T) == 2 ? 4 : 2)
 scale_transpose_vec_kernel(const __grid_constant__ NormTable tab, int nparts) {
   ptx_grid_dep_launch();
   const NormEntry& en = tab.e[blockIdx.y];
   const T* __restrict__ g = reinterpret_cast<const T*>(en.g);
-  const long long cols = en.cols, ldg = en.ldg;
+  const long long rows = en.rows, cols = en.cols, ldg = en.ldg;
   const float* __restrict__ partials = en.partials;
   __nv_bfloat16* __restrict__ xd = en.xd;
   __nv_bfloat16* __restrict__ xt = en.xt;
   const long long ldxd = en.ldxd, ldxt = en.ldxt;
+  constexpr int R = kScaleTileRows, C = 64;
   constexpr int V = 16 / sizeof(T);        // input elements per 16-byte load
-  constexpr int CHUNKS = 64 / V;           // loads per tile row
+  constexpr int CHUNKS = C / V;            // loads per tile row
+  constexpr int LOADS = (R * CHUNKS) / 256;
   __shared__ float red[8];
-  // 8-element column groups are XOR-swizzled with the row group, so that both the row-wise
-  // 16-byte stores and the column-wise gathers below are free of bank conflicts
-  __shared__ __align__(16) __nv_bfloat16 tile[64][64];
-  auto swz = [](int r, int c) { return (((c >> 3) ^ ((r >> 3) & 7)) << 3) | (c & 7); };
-  const long long tiles_c = cols / 64;
-  const long long tr = blockIdx.x / tiles_c, tc = blockIdx.x - tr * tiles_c;
-  const long long r0 = tr * 64, c0 = tc * 64;
-  constexpr int LOADS = (64 * CHUNKS) / 256;
-  // the tile's loads go out first; folding the partial sums hides under their latency
-  uint4 raw[LOADS];
+  // Staging tile, [R][C] bf16 = [R][32] words.  The 8-element column groups of a row are
+  // XOR-swizzled with the row group, and the halves of a group are swapped in rows >= 64 (rows r
+  // and r + 64 share a group), so that both the row-wise 16-byte stores and the column-wise
+  // 4-byte gathers below are free of bank conflicts.
+  __shared__ __align__(16) uint32_t tile[R][C / 2];
+  auto swz = [](int r, int c) {  // element column c of row r -> element position in the row
+    return (((c >> 3) ^ ((r >> 3) & 7)) << 3) | ((c & 7) ^ (((r >> 6) & 1) << 2));
+  };
+  const long long tiles_c = cols / C;
+  const long long tiles = ((rows + R - 1) / R) * tiles_c;
+
+  uint4 raw[LOADS], nxt[LOADS];
+  auto fetch = [&](long long t, uint4* dst) {
+    const long long tr = t / tiles_c, tc = t - tr * tiles_c;
+    const long long r0 = tr * R, c0 = tc * C;
 #pragma unroll
-  for (int i = 0; i < LOADS; ++i) {
-    const int idx = threadIdx.x + i * 256;
-    const int rr = idx / CHUNKS, cc = (idx % CHUNKS) * V;
-    raw[i] = __ldg(reinterpret_cast<const uint4*>(g + (r0 + rr) * ldg + c0 + cc));
-  }
+    for (int i = 0; i < LOADS; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      const int rr = idx / CHUNKS, cc = (idx % CHUNKS) * V;
+      dst[i] = (r0 + rr < rows) ? __ldg(reinterpret_cast<const uint4*>(g + (r0 + rr) * ldg + c0 + cc))
+                                : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  long long t = blockIdx.x;
+  // the first tile's loads go out first; folding the partial sums hides under their latency
+  if (t < tiles) fetch(t, raw);
   float s = 0.f;
   for (int i = threadIdx.x; i < nparts; i += 256) s += partials[i];
   const float total = block_sum_256(s, red);
+  // torch: norm -> bf16, (+1e-7) -> bf16, x / that -> bf16  (flash_muon/muon.py:23)
   const float d = __bfloat162float(__float2bfloat16_rn(sqrtf(total)));
   const float dp = __bfloat162float(__float2bfloat16_rn(d + 1e-7f));
+  const float rdp = 1.f / dp;
 
+  for (; t < tiles; t += gridDim.x) {
+    const long long tn = t + gridDim.x;
+    if (tn < tiles) fetch(tn, nxt);
+    const long long tr = t / tiles_c, tc = t - tr * tiles_c;
+    const long long r0 = tr * R, c0 = tc * C;
 #pragma unroll
-  for (int i = 0; i < LOADS; ++i) {
-    const int idx = threadIdx.x + i * 256;
-    const int rr = idx / CHUNKS, cc = (idx % CHUNKS) * V;
-    const T* e = reinterpret_cast<const T*>(&raw[i]);
-    alignas(16) __nv_bfloat16 q[V];
+    for (int i = 0; i < LOADS; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      const int rr = idx / CHUNKS, cc = (idx % CHUNKS) * V;
+      const T* e = reinterpret_cast<const T*>(&raw[i]);
+      // x * (1 / dp) is within 3 fp32 ulps of the correctly rounded x / dp, so both round to the
+      // same bf16 value unless the product lies within a few ulps of the midpoint between two
+      // bf16 values (low 16 bits near 0x8000); only then is the division carried out.
+      float y[V];
+      bool near_mid = false;
 #pragma unroll
-    for (int j = 0; j < V; ++j) q[j] = __float2bfloat16_rn(as_bf16_value<T>(e[j]) / dp);
-    if (xd != nullptr) {
-      if (V == 8) *reinterpret_cast<uint4*>(xd + (r0 + rr) * ldxd + c0 + cc) = *reinterpret_cast<uint4*>(q);
-      else *reinterpret_cast<uint2*>(xd + (r0 + rr) * ldxd + c0 + cc) = *reinterpret_cast<uint2*>(q);
+      for (int j = 0; j < V; ++j) {
+        y[j] = as_bf16_value<T>(e[j]) * rdp;
+        near_mid |= ((__float_as_uint(y[j]) + 0x10u) & 0xffe0u) == 0x8000u;
+      }
+      if (near_mid) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) y[j] = as_bf16_value<T>(e[j]) / dp;
+      }
+      alignas(16) __nv_bfloat162 q[V / 2];
+#pragma unroll
+      for (int j = 0; j < V / 2; ++j) q[j] = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+      if (xd != nullptr && r0 + rr < rows) {
+        if (V == 8) *reinterpret_cast<uint4*>(xd + (r0 + rr) * ldxd + c0 + cc) = *reinterpret_cast<uint4*>(q);
+        else *reinterpret_cast<uint2*>(xd + (r0 + rr) * ldxd + c0 + cc) = *reinterpret_cast<uint2*>(q);
+      }
+      if (V == 8) {
+        const uint4 v = *reinterpret_cast<uint4*>(q);
+        *reinterpret_cast<uint4*>(&tile[rr][(swz(rr, cc) & ~7) >> 1]) =
+            (rr & 64) ? make_uint4(v.z, v.w, v.x, v.y) : v;
+      } else {
+        *reinterpret_cast<uint2*>(&tile[rr][swz(rr, cc) >> 1]) = *reinterpret_cast<uint2*>(q);
+      }
     }
-    if (V == 8) *reinterpret_cast<uint4*>(&tile[rr][swz(rr, cc)]) = *reinterpret_cast<uint4*>(q);
-    else *reinterpret_cast<uint2*>(&tile[rr][swz(rr, cc)]) = *reinterpret_cast<uint2*>(q);
-  }
-  if (xt == nullptr) return;
-  __syncthreads();
+    if (xt != nullptr) {
+      __syncthreads();
+      // A thread takes two neighbouring columns (one 4-byte word per row) of 8 rows and writes
+      // two 16-byte vectors of the transposed copy.
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int idx = threadIdx.x + i * 256;   // 64 output rows x 8 chunks of 8 elements
-    const int cc = idx >> 3, rs = (idx & 7) * 8;
-    alignas(16) __nv_bfloat16 q[8];
+      for (int i = 0; i < (R * C) / (256 * 16); ++i) {
+        const int idx = threadIdx.x + i * 256;   // C/2 column pairs x R/8 row groups
+        const int cp = idx / (R / 8), rs = (idx % (R / 8)) * 8;
+        const int word = swz(rs, 2 * cp) >> 1;   // the same for the 8 rows of a group
+        uint32_t w[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) q[e] = tile[rs + e][swz(rs + e, cc)];
-    *reinterpret_cast<uint4*>(xt + (c0 + cc) * ldxt + r0 + rs) = *reinterpret_cast<uint4*>(q);
+        for (int e = 0; e < 8; ++e) w[e] = tile[rs + e][word];
+        if (r0 + rs < rows) {
+          uint4 lo, hi;
+          lo.x = __byte_perm(w[0], w[1], 0x5410); hi.x = __byte_perm(w[0], w[1], 0x7632);
+          lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
+          lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
+          lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
+          __nv_bfloat16* dst = xt + (c0 + 2 * cp) * ldxt + r0 + rs;
+          *reinterpret_cast<uint4*>(dst) = lo;
+          *reinterpret_cast<uint4*>(dst + ldxt) = hi;
+        }
+      }
+      __syncthreads();  // the next tile overwrites the staging tile
+    }
+#pragma unroll
+    for (int i = 0; i < LOADS; ++i) raw[i] = nxt[i];
   }
 }
 
@@ -411,12 +474,27 @@ int normalize_batch_t(const NormTable& tab, int count, bool sumsq_ready, cudaStr
            (e.xd == nullptr || (e.ldxd % 8 == 0 && (reinterpret_cast<uintptr_t>(e.xd) & 15u) == 0)) &&
            (e.xt == nullptr || (e.ldxt % 8 == 0 && (reinterpret_cast<uintptr_t>(e.xt) & 15u) == 0));
   }
-  const dim3 grid((unsigned)tiles, (unsigned)count);
   const int nparts = norm_blocks(rows * cols);
-  if (fast)
-    scale_transpose_vec_kernel<T><<<grid, 256, 0, stream>>>(tab, nparts);
-  else
-    scale_transpose_kernel<T><<<grid, 256, 0, stream>>>(tab, nparts);
+  if (fast) {
+    // one tile per block while that is at most two rounds of resident blocks; beyond that as
+    // many blocks as are resident at once, every one walking the same number of tiles
+    static long long resident = 0;
+    if (resident == 0) {
+      int per_sm = 0;
+      FM_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, scale_transpose_vec_kernel<T>, 256, 0));
+      resident = (long long)(per_sm > 0 ? per_sm : 1) * sm_count();
+    }
+    const long long per = ((rows + kScaleTileRows - 1) / kScaleTileRows) * (cols / 64);
+    long long blocks = per;
+    if (per * count > 2 * resident) {
+      const long long share = resident / count > 0 ? resident / count : 1;
+      const long long tiles_per_block = (per + share - 1) / share;
+      blocks = (per + tiles_per_block - 1) / tiles_per_block;
+    }
+    scale_transpose_vec_kernel<T><<<dim3((unsigned)blocks, (unsigned)count), 256, 0, stream>>>(tab, nparts);
+  } else {
+    scale_transpose_kernel<T><<<dim3((unsigned)tiles, (unsigned)count), 256, 0, stream>>>(tab, nparts);
+  }
   FM_CUDA_CHECK(cudaGetLastError());
   return FM_OK;
 }

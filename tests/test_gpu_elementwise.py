@@ -112,3 +112,26 @@ def test_normalize_bit_exact(dt, rows, cols):
     assert torch.equal(xt[:, :rows], xd[:, :cols].T)
     assert torch.isnan(xd[:, cols:]).all() and torch.isnan(xt[:, rows:]).all()
     _lib.device_status()
+
+
+@pytest.mark.parametrize("rows,cols", [(192, 320), (2048, 2048), (4096, 1024), (64, 8192)])
+def test_normalize_quotients_are_correctly_rounded_divisions(rows, cols):
+    """The 16-byte path multiplies by the reciprocal of the denominator and divides only where the
+    product lies near a bf16 rounding boundary.  Every element must still be the fp32 quotient
+    rounded to bf16, as torch's division gives it (flash_muon/muon.py:23), for the bf16 denominator
+    the kernel derived: torch's own, or its neighbour when the sum order moved the last bit."""
+    X = _rand(rows * cols, torch.bfloat16, 1.0, 7 * rows + cols).view(rows, cols)
+    xd = torch.empty_like(X)
+    xt = torch.empty(cols, rows, device=DEV, dtype=torch.bfloat16)
+    part = torch.empty(lib.fm_norm_scratch_floats(), device=DEV, dtype=torch.float32)
+    check(lib.fm_normalize(X.data_ptr(), rows, cols, cols, dtype_code(torch.bfloat16), xd.data_ptr(), cols,
+                           xt.data_ptr(), rows, part.data_ptr(), 0))
+    norm = X.norm(dim=(-2, -1), keepdim=True)
+    bits = norm.view(torch.int16)
+    hits = []
+    for delta in (0, -1, 1):
+        d = (bits + delta).view(torch.bfloat16)
+        hits.append(torch.equal(xd, X / (d + 1e-7)))
+    assert any(hits), "no bf16 denominator next to torch's reproduces the kernel's quotients"
+    assert torch.equal(xt, xd.T)
+    _lib.device_status()
