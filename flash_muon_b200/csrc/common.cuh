@@ -39,7 +39,7 @@ int encode_tmap_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner
 // a launch path calls getenv.
 struct Options {
   int gemm_impl = 0;     // 0: by tile count; 1: single-CTA kernel; 2: CTA-pair kernel
-  int gemm_bn = 0;       // single-CTA kernel: 0 by tile count, 128 or 256
+  int gemm_bn = 0;       // single-CTA kernel: 0 by tile count, 64, 128 or 256
   int gemm_stages = 0;   // CTA-pair kernel: 0 = default ring depth, else 2..7
   int gemm_balance = 1;  // 0: never cut the tail of a tile list by K blocks
   int gemm_strip = -1;   // symmetric lists of the pair kernel: -1 by size, 0 column order, w strips

@@ -35,7 +35,7 @@ constexpr int kSlabBytes = 128 * BK * 2;  // one 128-row operand slab = one TMA 
 
 template <int BN>
 struct Cfg {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kStageBytes = kSlabBytes + BN * BK * 2;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators of BN fp32 columns
   static constexpr int kNumBars = 2 * kStages + 4;
@@ -102,10 +102,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
         if (t + (int)gridDim.x >= p.num_tiles) ptx::grid_dep_launch();  // this CTA's last tile
         const Tile tl = decode_tile<BN>(p, t);
-        const int nb = tl.ncols >> 7;
+        // B arrives in boxes of min(BN, 128) rows (the box of tmB)
+        const int nb = BN < 128 ? 1 : (tl.ncols >> 7);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
-          ptx::mbar_expect_tx(full_bar(s), (uint32_t)(1 + nb) * kSlabBytes);
+          ptx::mbar_expect_tx(full_bar(s), (uint32_t)(kSlabBytes + tl.ncols * BK * 2));
           ptx::tma_load_2d(a_smem(s), &tmA, full_bar(s), kb * BK, tl.m0);
           for (int q = 0; q < nb; ++q)
             ptx::tma_load_2d(b_smem(s) + q * kSlabBytes, &tmB, full_bar(s), kb * BK,
@@ -350,19 +351,28 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
     return gemm_tc2_launch(a.dtype, tmA, tmB, tmC, tmT, p, a.sk_ws, a.sk_bytes, stream);
   }
 
-  // Tile width: 256 columns (less operand traffic per FLOP) unless that leaves most SMs idle.
+  // Tile width: 256 columns (less operand traffic per FLOP) unless that leaves most SMs idle;
+  // 64 columns when even 128 x 128 tiles occupy less than half of the SMs (what bounds such a
+  // launch is what one SM can load and store, so more, smaller units of work finish sooner).
   int bn = 256;
   const int sms = sm_count();
   if (count_tiles<256>(p.M, p.N, p.sym) < sms) bn = 128;
+  if (bn == 128 && 2 * count_tiles<128>(p.M, p.N, p.sym) <= sms) bn = 64;
   {
     const int v = options().gemm_bn;
-    if (v == 128 || v == 256) bn = v;
+    if (v == 64 || v == 128 || v == 256) bn = v;
+  }
+  if (bn == 64) {  // B in boxes of 64 rows
+    rc = encode_tmap_2d(&tmB, a.dtype, a.B, (uint64_t)a.K, rows_b, (uint64_t)a.ldb, BK, 64);
+    if (rc != FM_OK) return rc;
   }
   if (a.dtype == FM_BF16)
-    return bn == 256 ? launch<__nv_bfloat16, 256>(tmA, tmB, p, stream)
-                     : launch<__nv_bfloat16, 128>(tmA, tmB, p, stream);
-  return bn == 256 ? launch<__half, 256>(tmA, tmB, p, stream)
-                   : launch<__half, 128>(tmA, tmB, p, stream);
+    return bn == 256   ? launch<__nv_bfloat16, 256>(tmA, tmB, p, stream)
+           : bn == 128 ? launch<__nv_bfloat16, 128>(tmA, tmB, p, stream)
+                       : launch<__nv_bfloat16, 64>(tmA, tmB, p, stream);
+  return bn == 256   ? launch<__half, 256>(tmA, tmB, p, stream)
+         : bn == 128 ? launch<__half, 128>(tmA, tmB, p, stream)
+                     : launch<__half, 64>(tmA, tmB, p, stream);
 }
 
 size_t gemm_sk_bytes(int dtype, int64_t M, int64_t N, int64_t K, int sym) {

@@ -16,12 +16,12 @@
 namespace fm {
 
 // ---------------------------------------------------------------------------------------------
-// Single-CTA kernel: 128 x BN tiles (BN = 128 or 256).
+// Single-CTA kernel: 128 x BN tiles (BN = 64, 128 or 256).
 // ---------------------------------------------------------------------------------------------
 struct Tile {
   int m0;     // first output row
   int n0;     // first output column
-  int ncols;  // 128 or 256 (UMMA N)
+  int ncols;  // 64, 128 or 256 (UMMA N)
   int bi;     // 128-row block index (for the diagonal test)
 };
 
@@ -31,6 +31,13 @@ FM_HD long long tri_before(long long j) {
   return R == 1 ? j * (j + 1) / 2 : j * (j + 1);
 }
 
+// 64-wide tiles (BN = 64), symmetric lists: column tile j holds the row blocks i with
+// 128 i <= 64 j + 63, i.e. i <= j / 2.  Tiles before column tile j:
+FM_HD long long half_before(long long j) {
+  const long long a = j >> 1;
+  return (j & 1) ? (a + 1) * (a + 1) : a * (a + 1);
+}
+
 // Length of the tile list of the single-CTA kernel.
 template <int BN>
 FM_HD int count_tiles(long long M, long long N, int sym) {
@@ -38,6 +45,7 @@ FM_HD int count_tiles(long long M, long long N, int sym) {
   const int tiles_m = (int)((M + 127) / 128);
   const int tiles_n = (int)((N + BN - 1) / BN);
   if (!sym) return tiles_m * tiles_n;
+  if (BN < 128) return (int)half_before(tiles_n);
   int n = 0;
   for (int j = 0; j < tiles_n; ++j) n += (R * j + R < tiles_m) ? (R * j + R) : tiles_m;
   return n;
@@ -47,6 +55,23 @@ template <int BN, class P>
 FM_HD Tile decode_tile(const P& p, int t) {
   constexpr int R = BN / 128;
   Tile o;
+  if (BN < 128) {  // 128 x 64 tiles
+    int i, j;
+    if (!p.sym) {
+      j = t / p.tiles_m;
+      i = t - j * p.tiles_m;
+    } else {
+      j = (int)(2.f * sqrtf((float)t));
+      while (half_before(j + 1) <= t) ++j;
+      while (half_before(j) > t) --j;
+      i = t - (int)half_before(j);
+    }
+    o.m0 = i * 128;
+    o.bi = i;
+    o.n0 = j * BN;
+    o.ncols = BN;
+    return o;
+  }
   int nblk0;
   if (!p.sym) {
     const int tn = t / p.tiles_m;

@@ -54,7 +54,7 @@ int fm_version(void);
 /*
  * Process-wide tuning switches, for experiments and A/B comparisons (the defaults are the
  * product).  Names: "gemm_impl" (0 by size, 1 single-CTA kernel, 2 CTA-pair kernel), "gemm_bn"
- * (tile width of the single-CTA kernel: 0 by size, 128, 256), "gemm_stages" (ring depth of the
+ * (tile width of the single-CTA kernel: 0 by size, 64, 128, 256), "gemm_stages" (ring depth of the
  * pair kernel, 0 = default), "gemm_balance" (0: never cut the tail of a tile list by K blocks),
  * "gemm_strip" (tile order of symmetric lists: -1 by size, 0 column order, w = strips of w tile
  * columns), "pdl" (0: no programmatic dependent launch), "gemm_tma_store" (0: the pair kernel

@@ -74,6 +74,30 @@ void check_single(int M, int N, int sym) {
   ++g_checked;
 }
 
+// 128 x 64 tiles: every 128 x 64 block on or above the diagonal's 128-row block exactly once.
+void check_single_64(int M, int N, int sym) {
+  Sched p{};
+  p.M = M; p.N = N; p.sym = sym;
+  p.tiles_m = (M + 127) / 128;
+  p.num_tiles = fm::count_tiles<64>(M, N, sym);
+  const int bn = (N + 63) / 64;
+  std::vector<int> cover((size_t)p.tiles_m * bn, 0);
+  for (int t = 0; t < p.num_tiles; ++t) {
+    const fm::Tile tl = fm::decode_tile<64>(p, t);
+    REQUIRE(tl.m0 >= 0 && tl.m0 < M && tl.m0 % 128 == 0, "BN=64 M=%d N=%d sym=%d t=%d m0=%d", M, N, sym, t, tl.m0);
+    REQUIRE(tl.n0 >= 0 && tl.n0 < N && tl.n0 % 64 == 0, "BN=64 M=%d N=%d sym=%d t=%d n0=%d", M, N, sym, t, tl.n0);
+    REQUIRE(tl.ncols == 64 && tl.bi == tl.m0 / 128, "ncols=%d bi=%d", tl.ncols, tl.bi);
+    ++cover[(size_t)tl.bi * bn + tl.n0 / 64];
+  }
+  for (int bi = 0; bi < p.tiles_m; ++bi)
+    for (int bj = 0; bj < bn; ++bj) {
+      const int want = (sym && bj < 2 * bi) ? 0 : 1;
+      REQUIRE(cover[(size_t)bi * bn + bj] == want, "BN=64 M=%d N=%d sym=%d block (%d,%d) covered %d times",
+              M, N, sym, bi, bj, cover[(size_t)bi * bn + bj]);
+    }
+  ++g_checked;
+}
+
 void check_pair_list(int M, int N, int sym, int strip_w = 0, bool columns_first = false) {
   Sched p{};
   p.M = M; p.N = N; p.sym = sym; p.strip_w = strip_w;
@@ -186,6 +210,7 @@ int main() {
       if (sym) {
         check_single<128>(m, m, 1);
         check_single<256>(m, m, 1);
+        check_single_64(m, m, 1);
         check_pair_list(m, m, 1);
         for (int w : {1, 2, 3, 5, 8, 12, 64}) check_pair_list(m, m, 1, w);   // column strips
       } else {
@@ -193,6 +218,7 @@ int main() {
           if ((long long)m * n > 8192LL * 16384) continue;
           check_single<128>(m, n, 0);
           check_single<256>(m, n, 0);
+          check_single_64(m, n, 0);
           check_pair_list(m, n, 0);
           check_pair_list(m, n, 0, 0, true);
         }

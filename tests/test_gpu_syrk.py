@@ -70,12 +70,12 @@ ODD = [(1, 8), (7, 8), (8, 1), (100, 72), (129, 64), (257, 136), (130, 1000), (3
        (384, 320), (640, 64), (1000, 520)]
 
 
-@pytest.mark.parametrize("bn", ["128", "256", "pair"])
+@pytest.mark.parametrize("bn", ["64", "128", "256", "pair"])
 @pytest.mark.parametrize("m,k", ODD)
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
 def test_sizes_off_the_tile_grid(m, k, dt, bn, options):
-    """Every tile shape of the tensor-core family (single CTA 128x128 / 128x256, CTA pair
-    256x256) on sizes that are not multiples of any of them."""
+    """Every tile shape of the tensor-core family (single CTA 128x64 / 128x128 / 128x256, CTA
+    pair 256x256) on sizes that are not multiples of any of them."""
     if bn == "pair":
         options("gemm_impl", 2)
     else:
@@ -239,6 +239,37 @@ def test_pipeline_and_store_switches_change_no_bit(name, value, options):
     for a, b in zip(ref, got):
         assert not torch.isnan(a).any() and torch.equal(a, b)
     assert torch.equal(got[2], got[1].T)
+    _lib.device_status()
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_tile_shapes_change_no_bit(bn, options):
+    """A tile's shape decides who computes an output element, not the order of its sum over K:
+    the single-CTA kernel with 128 x 64, 128 x 128 and 128 x 256 tiles gives the bits of the
+    CTA-pair kernel, for a symmetric product and a general one with addend and both outputs."""
+    lib = _lib.lib
+    g = torch.Generator(device=DEV).manual_seed(37)
+    x = (torch.randn(900, 1096, device=DEV, generator=g) / 33).bfloat16()
+    M, N, K = 520, 712, 328
+    A = (torch.randn(M, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    B = torch.randn(N, K, device=DEV, generator=g).bfloat16()
+    D = torch.randn(M, N, device=DEV, generator=g).bfloat16()
+
+    def run():
+        y = fm.matmul_transpose(x)
+        C = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        CT = torch.full((N, M), float("nan"), device=DEV, dtype=torch.bfloat16)
+        _lib.check(lib.fm_gemm_nt(A.data_ptr(), K, B.data_ptr(), K, M, N, K, D.data_ptr(), N, 3.4445, 1.0,
+                                  C.data_ptr(), N, CT.data_ptr(), M, 0, 0, 0))
+        return y, C, CT
+
+    options("gemm_impl", 2)
+    ref = run()
+    options("gemm_impl", 1)
+    options("gemm_bn", bn)
+    got = run()
+    for a, b in zip(ref, got):
+        assert not torch.isnan(a).any() and torch.equal(a, b)
     _lib.device_status()
 
 
