@@ -391,6 +391,12 @@ class Muon(torch.optim.Optimizer):
             self._side = st = torch.cuda.Stream(device=device)
         return st
 
+    def _land_stream(self, device):
+        st = getattr(self, "_land", None)
+        if st is None or st.device != device:
+            self._land = st = torch.cuda.Stream(device=device)
+        return st
+
     @torch.no_grad()
     def step(self, *, grad_ready=None, on_applied=None):
         """One optimizer step (flash_muon/muon.py:75-110; no closure, returns None).
@@ -499,6 +505,8 @@ class Muon(torch.optim.Optimizer):
             device = self.param_groups[0]["update_buffer"].device
             main = torch.cuda.current_stream(device)
             side = self._side_stream(device)
+            land = self._land_stream(device)    # waits for what the peers push into this rank
+            land.wait_stream(main)
             if self._two_lanes:
                 extra = getattr(self, "_extra_lanes", None)
                 if extra is None or extra[0].device != device:
@@ -555,12 +563,16 @@ class Muon(torch.optim.Optimizer):
                         p_own = params[mine] if mine < len(params) else params[prev_base]
                         h = peer.publish(gi, prev, p_own.data_ptr(), p_own.numel() * p_own.element_size(),
                                          list(range(len(params_world))), param_index=mine)
+                        # the slot is free again once my own update has read it: nothing of this
+                        # rank's compute waits for a peer inside the step
+                        upd_done[prev] = torch.cuda.Event()
+                        upd_done[prev].record(side)
+                    with torch.cuda.stream(land):
                         h.wait()            # the peers' parameters of this round have landed here
                         h.done()
                         if on_applied is not None:
-                            on_applied(params_world, side)
-                        upd_done[prev] = torch.cuda.Event()
-                        upd_done[prev].record(side)
+                            land.wait_event(upd_done[prev])
+                            on_applied(params_world, land)
                     return
                 with torch.cuda.stream(side):
                     if handle is not None:
@@ -629,6 +641,7 @@ class Muon(torch.optim.Optimizer):
                 update_prev()
         if overlap:
             main.wait_stream(side)  # the step's effects are ordered on the caller's stream
+            main.wait_stream(land)
             if peer is not None:
                 peer.end_step(main)
             if lanes is not None:

@@ -46,6 +46,7 @@ release needs nothing from the peer that is gone.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 import time
 
@@ -190,8 +191,11 @@ class PeerGather:
         self._step_events: list = []
         ops.barrier()  # nobody writes a flag before everybody has zeroed and mapped them
         # peers in rotated order, so that the ranks of a box do not all push to rank 0 first
-        self.streams = {q: ops.new_stream()
-                        for q in ((rank + i) % world_size for i in range(1, world_size))}
+        # (FM_MUON_PEER_STREAMS=<n>: the copies to all peers share n streams instead of one each)
+        n_streams = int(os.environ.get("FM_MUON_PEER_STREAMS", "0")) or (world_size - 1)
+        pool = [ops.new_stream() for _ in range(max(1, min(n_streams, world_size - 1)))]
+        self.streams = {(rank + i) % world_size: pool[(i - 1) % len(pool)]
+                        for i in range(1, world_size)}
         self._release_stream = ops.new_stream()
         # host-side mirror of the use counters: seq[group][buffer][producer]
         self.seq = [[[0] * world_size for _ in range(self.nbuf)] for _ in range(self.ngroups)]
@@ -301,7 +305,8 @@ class PeerGather:
                 self.ops.copy(st, dst, slot_addr, nbytes)
                 self.ops.write32(st, self.flag_addr(q, gi, b, READY, self.rank), s)
                 ev = self.ops.record(st)
-                self.push_events[gi][b].append(ev)
+                if param_index is None:  # copies out of the slot: it may not be rewritten before
+                    self.push_events[gi][b].append(ev)
                 self._step_events.append(ev)
         return PeerRound(self, gi, b, producers, seqs)
 

@@ -291,6 +291,7 @@ def drive_params(ws, nbuf, lanes, seed, drop_step_wait=False, absent=(), timeout
         main = ops.cur
         lane_streams = [main] + [SimStream(sim, f"r{r}.lane{i}") for i in range(1, lanes)]
         side = SimStream(sim, f"r{r}.side")
+        land = SimStream(sim, f"r{r}.land")
         for step in range(steps):
             if (r, step) in absent:      # this rank left before the step: it enqueues nothing more
                 break
@@ -307,7 +308,7 @@ def drive_params(ws, nbuf, lanes, seed, drop_step_wait=False, absent=(), timeout
             pg.begin_step(main)
             if drop_step_wait:
                 pg._step_waited = set(range(ws))   # pretend every peer was already waited for
-            for st in lane_streams[1:]:
+            for st in lane_streams[1:] + [land]:
                 ops.wait_event(st, ops.record(main))
             upd_done = [None] * nbuf
             pending = None
@@ -325,11 +326,12 @@ def drive_params(ws, nbuf, lanes, seed, drop_step_wait=False, absent=(), timeout
                     lane.push(lambda: True, lambda: None)          # momentum + Newton-Schulz
                     ns_done = ops.record(lane)
                 if pending is not None:
-                    _flush(sim, ops, pg, side, pars, r, nbytes, pending, upd_done, step)
+                    _flush(sim, ops, pg, side, land, pars, r, nbytes, pending, upd_done, step)
                 pending = (b, base, world, mine, ns_done)
-            _flush(sim, ops, pg, side, pars, r, nbytes, pending, upd_done, step)
-            # join: side stream and pushes, then the step is over on main
+            _flush(sim, ops, pg, side, land, pars, r, nbytes, pending, upd_done, step)
+            # join: side stream, landing stream and pushes, then the step is over on main
             ops.wait_event(main, ops.record(side))
+            ops.wait_event(main, ops.record(land))
             pg.end_step(main)
 
             def check_end(r=r, step=step):
@@ -343,7 +345,9 @@ def drive_params(ws, nbuf, lanes, seed, drop_step_wait=False, absent=(), timeout
     sim.run()
 
 
-def _flush(sim, ops, pg, side, pars, r, nbytes, pending, upd_done, step):
+def _flush(sim, ops, pg, side, land, pars, r, nbytes, pending, upd_done, step):
+    """One round as Muon.step enqueues it: own update and pushes on the side stream (the slot is
+    free once the update has read it), waiting for the peers' pushes on the landing stream."""
     b, base, world, mine, ns_done = pending
     if ns_done is not None:
         ops.wait_event(side, ns_done)
@@ -355,9 +359,11 @@ def _flush(sim, ops, pg, side, pars, r, nbytes, pending, upd_done, step):
         side.push(lambda: True, own_update)
     src = pars[r][mine] if mine < nparams else pars[r][base]
     h = pg.publish(0, b, src, nbytes, list(range(len(world))), param_index=mine)
+    upd_done[b] = ops.record(side)
+    ops.cur = land
     h.wait()
     h.done()
-    upd_done[b] = ops.record(side)
+    ops.cur = side
 
 
 @pytest.mark.parametrize("ws,nbuf,lanes", [(2, 2, 1), (3, 4, 2), (4, 8, 4)])
