@@ -204,17 +204,26 @@ scale_transpose_vec_kernel(const __grid_constant__ NormTable tab, int nparts) {
   const long long tiles_c = cols / C;
   const long long tiles = ((rows + R - 1) / R) * tiles_c;
 
+  // Per-thread constants of the tile walk: the thread's column chunk is the same in all of its
+  // LOADS vectors, its rows are RSTEP apart; in the transposed phase its 8 rows are the same for
+  // all of its column pairs, which are 2 * PSTEP columns apart.
+  constexpr int RSTEP = 256 / CHUNKS;
+  constexpr int PSTEP = 256 / (R / 8);
+  const int rr0 = threadIdx.x / CHUNKS, cc = (threadIdx.x % CHUNKS) * V;
+  const int cp0 = threadIdx.x / (R / 8), rs = (threadIdx.x % (R / 8)) * 8;
+  const long long g_off = (long long)rr0 * ldg + cc, g_step = (long long)RSTEP * ldg;
+  const long long d_off = (long long)rr0 * ldxd + cc, d_step = (long long)RSTEP * ldxd;
+  const long long t_off = (long long)(2 * cp0) * ldxt + rs, t_step = (long long)(2 * PSTEP) * ldxt;
+
   uint4 raw[LOADS], nxt[LOADS];
   auto fetch = [&](long long t, uint4* dst) {
     const long long tr = t / tiles_c, tc = t - tr * tiles_c;
-    const long long r0 = tr * R, c0 = tc * C;
+    const long long r0 = tr * R;
+    const T* src = g + r0 * ldg + tc * C + g_off;
 #pragma unroll
-    for (int i = 0; i < LOADS; ++i) {
-      const int idx = threadIdx.x + i * 256;
-      const int rr = idx / CHUNKS, cc = (idx % CHUNKS) * V;
-      dst[i] = (r0 + rr < rows) ? __ldg(reinterpret_cast<const uint4*>(g + (r0 + rr) * ldg + c0 + cc))
-                                : make_uint4(0u, 0u, 0u, 0u);
-    }
+    for (int i = 0; i < LOADS; ++i)
+      dst[i] = (r0 + rr0 + i * RSTEP < rows) ? __ldg(reinterpret_cast<const uint4*>(src + i * g_step))
+                                             : make_uint4(0u, 0u, 0u, 0u);
   };
   long long t = blockIdx.x;
   // the first tile's loads go out first; folding the partial sums hides under their latency
@@ -232,22 +241,23 @@ scale_transpose_vec_kernel(const __grid_constant__ NormTable tab, int nparts) {
     if (tn < tiles) fetch(tn, nxt);
     const long long tr = t / tiles_c, tc = t - tr * tiles_c;
     const long long r0 = tr * R, c0 = tc * C;
+    __nv_bfloat16* const xd_t = xd + r0 * ldxd + c0 + d_off;
 #pragma unroll
     for (int i = 0; i < LOADS; ++i) {
-      const int idx = threadIdx.x + i * 256;
-      const int rr = idx / CHUNKS, cc = (idx % CHUNKS) * V;
+      const int rr = rr0 + i * RSTEP;
       const T* e = reinterpret_cast<const T*>(&raw[i]);
-      // x * (1 / dp) is within 3 fp32 ulps of the correctly rounded x / dp, so both round to the
-      // same bf16 value unless the product lies within a few ulps of the midpoint between two
-      // bf16 values (low 16 bits near 0x8000); only then is the division carried out.
+      // x * (1 / dp) lies within 2.5 fp32 ulps of x / dp, hence within 2 ulps of the correctly
+      // rounded quotient: both round to the same bf16 value unless the product is within 2 ulps
+      // of the midpoint between two bf16 values (low 16 bits 0x7ffe .. 0x8002).  A vector with an
+      // element whose low bits fall in 0x7ffc .. 0x8003 (one vector in 1000) takes the division.
       float y[V];
       bool near_mid = false;
 #pragma unroll
       for (int j = 0; j < V; ++j) {
         y[j] = as_bf16_value<T>(e[j]) * rdp;
-        near_mid |= ((__float_as_uint(y[j]) + 0x10u) & 0xffe0u) == 0x8000u;
+        near_mid |= ((__float_as_uint(y[j]) + 4u) & 0xfff8u) == 0x8000u;
       }
-      if (near_mid) {
+      if (near_mid) {  // one vector in 1000
 #pragma unroll
         for (int j = 0; j < V; ++j) y[j] = as_bf16_value<T>(e[j]) / dp;
       }
@@ -255,8 +265,8 @@ scale_transpose_vec_kernel(const __grid_constant__ NormTable tab, int nparts) {
 #pragma unroll
       for (int j = 0; j < V / 2; ++j) q[j] = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
       if (xd != nullptr && r0 + rr < rows) {
-        if (V == 8) *reinterpret_cast<uint4*>(xd + (r0 + rr) * ldxd + c0 + cc) = *reinterpret_cast<uint4*>(q);
-        else *reinterpret_cast<uint2*>(xd + (r0 + rr) * ldxd + c0 + cc) = *reinterpret_cast<uint2*>(q);
+        if (V == 8) *reinterpret_cast<uint4*>(xd_t + i * d_step) = *reinterpret_cast<uint4*>(q);
+        else *reinterpret_cast<uint2*>(xd_t + i * d_step) = *reinterpret_cast<uint2*>(q);
       }
       if (V == 8) {
         const uint4 v = *reinterpret_cast<uint4*>(q);
@@ -270,21 +280,21 @@ scale_transpose_vec_kernel(const __grid_constant__ NormTable tab, int nparts) {
       __syncthreads();
       // A thread takes two neighbouring columns (one 4-byte word per row) of 8 rows and writes
       // two 16-byte vectors of the transposed copy.
+      __nv_bfloat16* const xt_t = xt + c0 * ldxt + r0 + t_off;
 #pragma unroll
       for (int i = 0; i < (R * C) / (256 * 16); ++i) {
-        const int idx = threadIdx.x + i * 256;   // C/2 column pairs x R/8 row groups
-        const int cp = idx / (R / 8), rs = (idx % (R / 8)) * 8;
+        const int cp = cp0 + i * PSTEP;          // column pair; C/2 pairs x R/8 row groups
         const int word = swz(rs, 2 * cp) >> 1;   // the same for the 8 rows of a group
         uint32_t w[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) w[e] = tile[rs + e][word];
+        for (int e2 = 0; e2 < 8; ++e2) w[e2] = tile[rs + e2][word];
         if (r0 + rs < rows) {
           uint4 lo, hi;
           lo.x = __byte_perm(w[0], w[1], 0x5410); hi.x = __byte_perm(w[0], w[1], 0x7632);
           lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
           lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
           lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
-          __nv_bfloat16* dst = xt + (c0 + 2 * cp) * ldxt + r0 + rs;
+          __nv_bfloat16* dst = xt_t + i * t_step;
           *reinterpret_cast<uint4*>(dst) = lo;
           *reinterpret_cast<uint4*>(dst + ldxt) = hi;
         }

@@ -27,7 +27,9 @@ What differs is how the device work is issued:
   updated parameter into the replicas of its peers, instead of every rank gathering and applying
   every update.  That equals the reference only while all replicas hold the same bits before the
   step, which is checked once when the exchange is set up (a mismatch selects the gather of
-  updates, as does ``FM_MUON_EXCHANGE=updates``);
+  updates, as does ``FM_MUON_EXCHANGE=updates``).  The waits for what the peers push sit on a
+  landing stream that only the end of the step joins, so none of a rank's own work waits for a
+  peer inside a step;
 * with ``world_size == 1`` and no hooks the whole step is one C call (``fm_muon_step``), which
   does the stream and event bookkeeping of the round loop inside the library
   (``FM_MUON_NATIVE=0`` keeps the loop below).
