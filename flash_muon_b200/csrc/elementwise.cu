@@ -201,8 +201,9 @@ scale_transpose_vec_kernel(const __grid_constant__ NormTable tab, int nparts) {
   auto swz = [](int r, int c) {  // element column c of row r -> element position in the row
     return (((c >> 3) ^ ((r >> 3) & 7)) << 3) | ((c & 7) ^ (((r >> 6) & 1) << 2));
   };
-  const long long tiles_c = cols / C;
-  const long long tiles = ((rows + R - 1) / R) * tiles_c;
+  // (32-bit tile arithmetic: a 64-bit division per tile costs as much as the tile's conversions)
+  const unsigned tiles_c = (unsigned)(cols / C);
+  const unsigned tiles = (unsigned)((rows + R - 1) / R) * tiles_c;   // < 2^31, checked by the host
 
   // Per-thread constants of the tile walk: the thread's column chunk is the same in all of its
   // LOADS vectors, its rows are RSTEP apart; in the transposed phase its 8 rows are the same for
@@ -216,16 +217,16 @@ scale_transpose_vec_kernel(const __grid_constant__ NormTable tab, int nparts) {
   const long long t_off = (long long)(2 * cp0) * ldxt + rs, t_step = (long long)(2 * PSTEP) * ldxt;
 
   uint4 raw[LOADS], nxt[LOADS];
-  auto fetch = [&](long long t, uint4* dst) {
-    const long long tr = t / tiles_c, tc = t - tr * tiles_c;
-    const long long r0 = tr * R;
-    const T* src = g + r0 * ldg + tc * C + g_off;
+  auto fetch = [&](unsigned t, uint4* dst) {
+    const unsigned tr = t / tiles_c, tc = t - tr * tiles_c;
+    const long long r0 = (long long)tr * R;
+    const T* src = g + r0 * ldg + (long long)tc * C + g_off;
 #pragma unroll
     for (int i = 0; i < LOADS; ++i)
       dst[i] = (r0 + rr0 + i * RSTEP < rows) ? __ldg(reinterpret_cast<const uint4*>(src + i * g_step))
                                              : make_uint4(0u, 0u, 0u, 0u);
   };
-  long long t = blockIdx.x;
+  unsigned t = blockIdx.x;
   // the first tile's loads go out first; folding the partial sums hides under their latency
   if (t < tiles) fetch(t, raw);
   float s = 0.f;
@@ -237,10 +238,10 @@ scale_transpose_vec_kernel(const __grid_constant__ NormTable tab, int nparts) {
   const float rdp = 1.f / dp;
 
   for (; t < tiles; t += gridDim.x) {
-    const long long tn = t + gridDim.x;
+    const unsigned tn = t + gridDim.x;
     if (tn < tiles) fetch(tn, nxt);
-    const long long tr = t / tiles_c, tc = t - tr * tiles_c;
-    const long long r0 = tr * R, c0 = tc * C;
+    const unsigned tr = t / tiles_c, tc = t - tr * tiles_c;
+    const long long r0 = (long long)tr * R, c0 = (long long)tc * C;
     __nv_bfloat16* const xd_t = xd + r0 * ldxd + c0 + d_off;
 #pragma unroll
     for (int i = 0; i < LOADS; ++i) {
