@@ -260,6 +260,17 @@ def test_parameter_push_exchange_over_two_steps(ws, nbuf, lanes, seed):
     drive_params(ws, nbuf, lanes, seed)
 
 
+@pytest.mark.parametrize("streams", ["1", "2"])
+@pytest.mark.parametrize("seed", range(6))
+def test_shared_copy_streams_are_safe_and_finish(streams, seed, monkeypatch):
+    """FM_MUON_PEER_STREAMS: the copies to several peers share a stream, so a wait for one peer's
+    acknowledgement also holds back the copies to the others.  Both exchanges must still finish
+    (the simulator raises when streams are stuck) and stay safe."""
+    monkeypatch.setenv("FM_MUON_PEER_STREAMS", streams)
+    drive(4, 4, 2, seed)
+    drive_params(4, 4, 2, seed)
+
+
 def test_simulation_catches_pushes_that_do_not_wait_for_the_step_flag():
     caught = 0
     for seed in range(40):
