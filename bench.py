@@ -232,7 +232,7 @@ def recorded_traffic(m: int, k: int):
     if rec.get("source_hash") != gemm_source_hash():
         return None, f"capture {rec.get('commit')} predates the current kernel sources"
     if any(os.environ.get(v) for v in ("FM_GEMM_IMPL", "FM_GEMM_BN", "FM_GEMM_STAGES", "FM_GEMM_BALANCE",
-                                       "FM_GEMM_STRIP", "FM_PDL", "FM_PDL_TRIGGER", "FM_GEMM_TMA_STORE",
+                                       "FM_GEMM_STRIP", "FM_PDL", "FM_PDL_TRIGGER", "FM_GEMM_TMA_STORE", "FM_GEMM_TMA_D",
                                        "FM_GEMM_KB_PER_STAGE", "FM_GEMM_L2_PROMOTION")):
         return None, "tuning switches set"
     return rec["dram_bytes_read"] + rec["dram_bytes_written"], f"{rec['summary']} (commit {rec['commit']})"

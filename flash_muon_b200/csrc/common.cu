@@ -43,6 +43,7 @@ Options& options() {
     env("FM_GEMM_STRIP", &opt.gemm_strip);
     env("FM_PDL", &opt.pdl);
     env("FM_GEMM_TMA_STORE", &opt.gemm_tma_store);
+    env("FM_GEMM_TMA_D", &opt.gemm_tma_d);
     env("FM_GEMM_KB_PER_STAGE", &opt.gemm_kb_per_stage);
     env("FM_PDL_TRIGGER", &opt.pdl_trigger);
     env("FM_GEMM_L2_PROMOTION", &opt.gemm_l2_promotion);
@@ -61,6 +62,7 @@ int* option_slot(const char* name) {
   if (!strcmp(name, "gemm_strip")) return &o.gemm_strip;
   if (!strcmp(name, "pdl")) return &o.pdl;
   if (!strcmp(name, "gemm_tma_store")) return &o.gemm_tma_store;
+  if (!strcmp(name, "gemm_tma_d")) return &o.gemm_tma_d;
   if (!strcmp(name, "gemm_kb_per_stage")) return &o.gemm_kb_per_stage;
   if (!strcmp(name, "pdl_trigger")) return &o.pdl_trigger;
   if (!strcmp(name, "gemm_l2_promotion")) return &o.gemm_l2_promotion;

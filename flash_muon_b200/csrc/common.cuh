@@ -48,6 +48,7 @@ struct Options {
   int pdl_trigger = 0;   // when CTAs release the next kernel: 0 by schedule, 1 always early, 2 never
   int gemm_kb_per_stage = 2;  // pair kernel: 64-wide K blocks per pipeline stage (1..3)
   int gemm_tma_store = 1;  // 0: the pair kernel writes its outputs with per-lane global stores
+  int gemm_tma_d = 1;      // 0: the pair kernel fetches the addend with per-lane global loads
 };
 Options& options();
 

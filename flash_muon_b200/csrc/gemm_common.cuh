@@ -54,6 +54,8 @@ struct GemmParams {
   // product keep the register path (their element-wise mirror rule).
   int tma_store;
   int c_batch_rows, t_batch_rows;       // rows between consecutive problems in the C / CT maps
+  int tma_d;                            // pair kernel: the addend arrives by TMA tile loads
+  int d_batch_rows;                     // rows between consecutive problems in the D map
 };
 
 // Base pointers of one problem of a (possibly batched) launch.

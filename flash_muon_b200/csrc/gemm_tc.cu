@@ -299,7 +299,8 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   if (a.batch > 1 && p.use_c_tab && a.D && a.d_batch % 8 != 0) p.d_vec = 0;
   if (a.batch > 1 && p.use_c_tab && a.CT && a.t_batch % 2 != 0) p.t_pack = 0;
   p.tma_store = 0;
-  p.c_batch_rows = p.t_batch_rows = 0;
+  p.tma_d = 0;
+  p.c_batch_rows = p.t_batch_rows = p.d_batch_rows = 0;
   p.err = device_error_word();
   if (!p.err) return fail(FM_ERR_CUDA, "no current CUDA device");
 
@@ -348,7 +349,23 @@ int gemm_tc(const GemmArgs& a, cudaStream_t stream) {
                           (uint64_t)a.ldt_r, 32, 64, false) == FM_OK;
     clear_error();
     p.tma_store = ok ? 1 : 0;
-    return gemm_tc2_launch(a.dtype, tmA, tmB, tmC, tmT, p, a.sk_ws, a.sk_bytes, stream);
+    // The addend by TMA tile loads as well (into the staging tiles of the stores, which then
+    // carry C only; the transposed output goes back to per-lane stores): needs the tile stores
+    // and an addend TMA can address, stacked like C when the launch is a batch.
+    CUtensorMap tmD = tmA;
+    p.tma_d = 0;
+    p.d_batch_rows = 0;
+    bool okd = ok && options().gemm_tma_d && a.D != nullptr && addressable(a.D, a.ldd, 1) &&
+               (a.batch == 1 || a.d_batch % a.ldd == 0);
+    if (okd) {
+      p.d_batch_rows = a.batch > 1 ? (int)(a.d_batch / a.ldd) : 0;
+      okd = encode_tmap_2d(&tmD, a.dtype, a.D, (uint64_t)a.N,
+                           (uint64_t)(a.batch - 1) * (uint64_t)p.d_batch_rows + (uint64_t)a.M,
+                           (uint64_t)a.ldd, 64, 32, true) == FM_OK;
+      clear_error();
+    }
+    p.tma_d = okd ? 1 : 0;
+    return gemm_tc2_launch(a.dtype, tmA, tmB, tmC, tmT, tmD, p, a.sk_ws, a.sk_bytes, stream);
   }
 
   // Tile width: 256 columns (less operand traffic per FLOP) unless that leaves most SMs idle;

@@ -50,8 +50,8 @@ struct GemmParams;
 int gemm_tc2_tiles(int64_t M, int64_t N, int sym);
 int gemm_tc2_max_pairs(int dtype);
 int gemm_tc2_launch(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                    const CUtensorMap& tmC, const CUtensorMap& tmT, GemmParams& p, void* sk_ws,
-                    size_t sk_bytes, cudaStream_t stream);
+                    const CUtensorMap& tmC, const CUtensorMap& tmT, const CUtensorMap& tmD,
+                    GemmParams& p, void* sk_ws, size_t sk_bytes, cudaStream_t stream);
 size_t gemm_tc2_sk_bytes(int dtype, int64_t M, int64_t N, int64_t K, int sym);
 
 // Exact-fp32 FFMA symmetric rank-k update for f32 inputs and layouts TMA cannot address.

@@ -49,7 +49,7 @@ constexpr int kMaxStages = 7;
 constexpr int kDefaultStages = 6;
 constexpr int kStageBytes = 2 * kSlabBytes;   // this CTA's A slab + B slab
 constexpr int kTmemCols = 512;                // two accumulators of 256 fp32 columns
-constexpr int kNumBars = 2 * kMaxStages + 4;
+constexpr int kNumBars = 2 * kMaxStages + 4 + 8;  // + two addend barriers per epilogue warp
 // staging of the TMA stores: per epilogue warp 32 x 64 values row-wise (4 KiB) and transposed (4 KiB)
 constexpr int kStagingBytes = 4 * 8192;
 constexpr int kMaxStagesWithStaging = 6;
@@ -85,7 +85,7 @@ template <typename T, bool kSplitK>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmT,
-                const __grid_constant__ GemmParams p) {
+                const __grid_constant__ CUtensorMap tmD, const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -104,6 +104,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
+  auto dfull_bar = [&](int q, int b) { return bar_base + 8u * (2 * kMaxStages + 4 + 2 * q + b); };
   auto a_smem = [&](int s) { return smem_base + s * kStageBytes; };
   auto b_smem = [&](int s) { return smem_base + s * kStageBytes + kSlabBytes; };
 
@@ -122,6 +123,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       ptx::mbar_init(tfull_bar(a), 1);
       ptx::mbar_init(tempty_bar(a), 8);  // 4 epilogue warps of each of the two CTAs
     }
+    for (int q = 0; q < 4; ++q)
+      for (int b = 0; b < 2; ++b) ptx::mbar_init(dfull_bar(q, b), 1);
     *abort_flag = 0;
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&tmA);
@@ -130,6 +133,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (p.C != nullptr) ptx::prefetch_tmap(&tmC);
       if (p.CT != nullptr) ptx::prefetch_tmap(&tmT);
     }
+    if (p.tma_d) ptx::prefetch_tmap(&tmD);
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
@@ -285,7 +289,19 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // one whose loads go out now.
       constexpr int kAhead = kSplitK ? 1 : 2;  // measured: 3 and 4 are slower again at K = 1024
       alignas(16) T dq[kAhead + 1][32];
-      if (!deposit) {
+      // Addend by TMA (whole-tile instantiation, tiles that leave through tile stores): the
+      // warp's two 4 KB staging tiles take turns as landing buffer of the addend's next 32 x 64
+      // block; the block is computed on in place and stored from there.
+      const bool d_tma = !kSplitK && p.tma_d != 0 && tma_tile && ep.D != nullptr;
+      if (d_tma) {
+        if (lane == 0) {
+          ptx::bulk_wait_read_all();  // stores of the previous tile have let go of the tiles
+          ptx::mbar_expect_tx(dfull_bar(q, 0), 4096u);
+          ptx::tma_load_2d(ptx::smem_u32(sC), &tmD, dfull_bar(q, 0), tl.n0,
+                           tr.g * p.d_batch_rows + row0w);
+        }
+        __syncwarp();
+      } else if (!deposit) {
 #pragma unroll
         for (int a = 0; a < kAhead; ++a) epilogue_load_d<T>(p, ep, row, tl.n0 + a * 32, dq[a]);
       }
@@ -342,7 +358,59 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (!ok) break;
       ptx::tc_fence_after();
       const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 256);
-      if (!deposit) {
+      if (d_tma) {
+        EpiPtrs ept = ep;   // the transposed output leaves through per-lane stores
+        ept.C = nullptr;
+        bool okd = true;
+#pragma unroll 1
+        for (int jp = 0; jp < 4 && okd; ++jp) {
+          const int b = jp & 1;
+          uint8_t* const cur = b ? sT : sC;
+          uint8_t* const oth = b ? sC : sT;
+          if (jp + 1 < 4) {  // the next block of the addend into the other tile
+            if (lane == 0) {
+              ptx::bulk_wait_read_all();  // the store that read the other tile (if any) is done
+              ptx::mbar_expect_tx(dfull_bar(q, b ^ 1), 4096u);
+              ptx::tma_load_2d(ptx::smem_u32(oth), &tmD, dfull_bar(q, b ^ 1), tl.n0 + (jp + 1) * 64,
+                               tr.g * p.d_batch_rows + row0w);
+            }
+            __syncwarp();
+          }
+          // every tile uses each barrier twice: use k of a tile waits for parity k
+          okd = ptx::mbar_wait(dfull_bar(q, b), (uint32_t)(jp >> 1), abort_flag);
+          okd = __all_sync(0xffffffffu, okd);
+          if (!okd) break;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int ch = 2 * jp + half;
+            const int c0 = tl.n0 + ch * 32;
+            uint32_t raw[32];
+            ptx::tmem_ld_32x32(t_acc + (uint32_t)(ch * 32), raw);
+            alignas(16) T dv[32];
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              reinterpret_cast<uint4*>(dv)[v] = *reinterpret_cast<const uint4*>(
+                  cur + lane * 128 + (((half * 4 + v) ^ (lane & 7)) * 16));
+            ptx::tmem_ld_wait();
+            if (row0w < p.M && c0 < p.N) {  // warp-uniform
+              alignas(16) T outv[32];
+              epilogue_values<T>(p, ep, raw, dv, outv);
+              if (ep.C != nullptr) epilogue_stage<T>(outv, cur, cur, lane, half, true, false);
+              if (ep.CT != nullptr) epilogue_store_regs<T>(p, ept, outv, row, c0, bi);
+            }
+          }
+          if (ep.C != nullptr) {
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            const int cx = tl.n0 + jp * 64;
+            if (lane == 0 && row0w < p.M && cx < p.N) {
+              ptx::tma_store_2d(&tmC, ptx::smem_u32(cur), cx, tr.g * p.c_batch_rows + row0w);
+              ptx::bulk_commit();
+            }
+          }
+        }
+        if (!okd) break;
+      } else if (!deposit) {
 #pragma unroll 1
         for (int ch = 0; ch < 8; ++ch) {
           uint32_t raw[32];
@@ -508,8 +576,8 @@ bool balance_plan(int tiles, int num_kb, int max_pairs, int batch, int* dp_tiles
 
 template <typename T>
 int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-            const CUtensorMap& tmT, GemmParams& p, int max_pairs, void* sk_ws, size_t sk_bytes,
-            cudaStream_t stream) {
+            const CUtensorMap& tmT, const CUtensorMap& tmD, GemmParams& p, int max_pairs,
+            void* sk_ws, size_t sk_bytes, cudaStream_t stream) {
   const int T_all = p.num_tiles;
   int pairs = T_all < max_pairs ? T_all : max_pairs;
   p.sk_dp_tiles = T_all;
@@ -558,10 +626,12 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& t
     cfg.numAttrs = 2;
   }
   cfg.attrs = attr;
-  if (p.sk_per > 0)
-    FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T, true>, tmA, tmB, tmC, tmT, p));
-  else
-    FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T, false>, tmA, tmB, tmC, tmT, p));
+  if (p.sk_per > 0) {
+    p.tma_d = 0;  // the instantiation with partial sums keeps the per-lane addend loads
+    FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T, true>, tmA, tmB, tmC, tmT, tmD, p));
+  } else {
+    FM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T, false>, tmA, tmB, tmC, tmT, tmD, p));
+  }
   return FM_OK;
 }
 
@@ -587,8 +657,8 @@ size_t gemm_tc2_sk_bytes(int dtype, int64_t M, int64_t N, int64_t K, int sym) {
 
 // `p` arrives filled except for the schedule fields, which depend on the tile shape.
 int gemm_tc2_launch(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                    const CUtensorMap& tmC, const CUtensorMap& tmT, GemmParams& p, void* sk_ws,
-                    size_t sk_bytes, cudaStream_t stream) {
+                    const CUtensorMap& tmC, const CUtensorMap& tmT, const CUtensorMap& tmD,
+                    GemmParams& p, void* sk_ws, size_t sk_bytes, cudaStream_t stream) {
   p.tiles_m = (p.M + 255) / 256;
   {
     const int tn = (p.N + 255) / 256;
@@ -600,8 +670,8 @@ int gemm_tc2_launch(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
   const int max_pairs = gemm_tc2_max_pairs(dtype);
   if (max_pairs <= 0) return fail(FM_ERR_CUDA, "no resident CTA pair possible for the GEMM kernel");
   return dtype == FM_BF16
-             ? launch2<__nv_bfloat16>(tmA, tmB, tmC, tmT, p, max_pairs, sk_ws, sk_bytes, stream)
-             : launch2<__half>(tmA, tmB, tmC, tmT, p, max_pairs, sk_ws, sk_bytes, stream);
+             ? launch2<__nv_bfloat16>(tmA, tmB, tmC, tmT, tmD, p, max_pairs, sk_ws, sk_bytes, stream)
+             : launch2<__half>(tmA, tmB, tmC, tmT, tmD, p, max_pairs, sk_ws, sk_bytes, stream);
 }
 
 }  // namespace fm

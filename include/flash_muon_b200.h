@@ -58,9 +58,10 @@ int fm_version(void);
  * pair kernel, 0 = default), "gemm_balance" (0: never cut the tail of a tile list by K blocks),
  * "gemm_strip" (tile order of symmetric lists: -1 by size, 0 column order, w = strips of w tile
  * columns), "pdl" (0: no programmatic dependent launch), "gemm_tma_store" (0: the pair kernel
- * writes its outputs with per-lane global stores instead of TMA tile stores).  Initial values come
+ * writes its outputs with per-lane global stores instead of TMA tile stores), "gemm_tma_d" (0: it
+ * fetches the addend with per-lane global loads instead of TMA tile loads).  Initial values come
  * from the environment variables FM_GEMM_IMPL, FM_GEMM_BN, FM_GEMM_STAGES, FM_GEMM_BALANCE,
- * FM_GEMM_STRIP, FM_PDL and FM_GEMM_TMA_STORE, read once.  Stands in for the autotune table of the reference
+ * FM_GEMM_STRIP, FM_PDL, FM_GEMM_TMA_STORE and FM_GEMM_TMA_D, read once.  Stands in for the autotune table of the reference
  * (flash_muon/matmul_transpose_triton.py:6-18); not thread-safe against concurrent launches.
  */
 int fm_set_option(const char* name, int value);

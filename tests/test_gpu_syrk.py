@@ -211,7 +211,7 @@ def test_dependent_launches_see_their_predecessor(pdl, options):
 
 @pytest.mark.parametrize("name,value", [("gemm_kb_per_stage", 1), ("gemm_kb_per_stage", 3), ("gemm_stages", 4),
                                         ("gemm_stages", 7), ("gemm_tma_store", 0), ("pdl_trigger", 1),
-                                        ("pdl_trigger", 2), ("pdl", 0), ("gemm_l2_promotion", 0)])
+                                        ("pdl_trigger", 2), ("pdl", 0), ("gemm_l2_promotion", 0), ("gemm_tma_d", 0)])
 def test_pipeline_and_store_switches_change_no_bit(name, value, options):
     """Ring depth, K blocks per stage, TMA or per-lane stores, dependent-launch trigger: all of
     them change how a tile is fed and written, none the order of any sum.  Symmetric product with
