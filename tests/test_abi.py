@@ -39,6 +39,16 @@ def test_library_exports(name):
     assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
 
 
+def test_integration_notes_name_every_entry_point():
+    """Every function the header declares has a line in INTEGRATION.md saying what it replaces."""
+    header = (ROOT / "include" / "flash_muon_b200.h").read_text()
+    notes = (ROOT / "INTEGRATION.md").read_text()
+    declared = sorted(set(re.findall(r"\b(fm_[a-z0-9_]+)\s*\(", header)))
+    assert declared, "no declarations found"
+    missing = [name for name in declared if name not in notes]
+    assert not missing, f"not in INTEGRATION.md: {missing}"
+
+
 def test_ctypes_table_has_no_undeclared_entry():
     from flash_muon_b200 import _lib
     assert sorted(_lib.SIGNATURES) == declared_symbols()

@@ -263,3 +263,34 @@ def test_state_dict_has_the_reference_layout_and_reference_checkpoints_load():
     opt2.load_state_dict(wide)
     assert all(tuple(g["update_buffer"].shape) == (1, g["params"][0].numel()) for g in opt2.param_groups)
     opt2.step()
+
+
+def test_matrices_per_pass_of_the_benchmark_shapes(monkeypatch):
+    """How many matrices of a numel group share one Newton-Schulz pass in the single-call step:
+    as many as fill two waves of 74 CTA pairs with the tiles of X @ X.T for narrow matrices
+    (1024 rows: 10 tiles each -> 14), two at a time for matrices that fill the GPU alone, two
+    lanes each; the environment overrides are honoured and clamped."""
+    for name in ("FM_MUON_BATCH", "FM_MUON_BATCH_LARGE", "FM_MUON_LANES"):
+        monkeypatch.delenv(name, raising=False)
+    shapes = [(1024, 1024), (4096, 1024), (1024, 4096), (2048, 2048), (4096, 4096), (4096, 14336)]
+    params = [torch.nn.Parameter(torch.empty(*s, dtype=torch.bfloat16)) for s in shapes]
+
+    class CpuMuon(fm.Muon):
+        _buffer_device = "cpu"      # the reference allocates on "cuda" (flash_muon/muon.py:69)
+
+    opt = CpuMuon(params, rank=0, world_size=1)
+    plans = {}
+    for group in opt.param_groups:
+        narrow = opt._narrow(group)
+        plans[narrow] = opt._plan(group, True)
+        assert opt._plan(group, False)[1] == 1            # the round loop's own plan: one per round
+    assert plans[1024] == (2, 14)
+    assert plans[2048] == (2, 4)
+    assert plans[4096] == (2, 2)
+    monkeypatch.setenv("FM_MUON_BATCH", "99")
+    monkeypatch.setenv("FM_MUON_BATCH_LARGE", "1")
+    monkeypatch.setenv("FM_MUON_LANES", "3")
+    for group in opt.param_groups:
+        lanes, batch = opt._plan(group, True)
+        assert lanes == 3
+        assert batch == (16 if opt._narrow(group) <= 2048 else 1)
